@@ -1,0 +1,182 @@
+// C ABI of fstattn_b200: argument checks and kernel dispatch.  See include/fstattn_b200.h.
+#include <cstdio>
+
+#include "fst_common.cuh"
+
+namespace fst {
+cudaError_t launch_mma_f16_d64(const AttnArgs &, int, cudaStream_t);
+cudaError_t launch_mma_f16_d128(const AttnArgs &, int, cudaStream_t);
+cudaError_t launch_mma_bf16_d64(const AttnArgs &, int, cudaStream_t);
+cudaError_t launch_mma_bf16_d128(const AttnArgs &, int, cudaStream_t);
+
+cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int tile_rows, cudaStream_t stream) {
+    if (dtype == FST_F16 && a.D == 64) return launch_mma_f16_d64(a, tile_rows, stream);
+    if (dtype == FST_F16 && a.D == 128) return launch_mma_f16_d128(a, tile_rows, stream);
+    if (dtype == FST_BF16 && a.D == 64) return launch_mma_bf16_d64(a, tile_rows, stream);
+    if (dtype == FST_BF16 && a.D == 128) return launch_mma_bf16_d128(a, tile_rows, stream);
+    return cudaErrorNotSupported;
+}
+
+static int elem_size(int dtype) { return dtype == FST_F32 ? 4 : 2; }
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static bool mma_ok(int dtype, int D, int bm) {
+    return (dtype == FST_F16 || dtype == FST_BF16) && (D == 64 || D == 128) &&
+           (bm == 16 || bm == 32 || bm == 64 || bm == 128);
+}
+
+static int cuda_status(cudaError_t e) {
+    if (e == cudaSuccess) return FST_OK;
+    if (e == cudaErrorNotSupported) return FST_ERR_UNSUPPORTED;
+    return FST_ERR_CUDA;
+}
+}  // namespace fst
+
+using namespace fst;
+
+extern "C" {
+
+int fst_version(void) { return FST_VERSION; }
+
+const char *fst_status_string(int s) {
+    switch (s) {
+        case FST_OK: return "ok";
+        case FST_ERR_INVALID_ARG: return "invalid argument";
+        case FST_ERR_UNSUPPORTED: return "unsupported dtype / head_dim / block_m combination";
+        case FST_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+        case FST_ERR_WORKSPACE: return "workspace too small";
+        case FST_ERR_CUDA: return "CUDA runtime error";
+        case FST_ERR_TOO_LARGE: return "size beyond the supported limit";
+        case FST_DEV_MALFORMED_TREE: return "malformed tree: parent[i] must be -1 or an earlier node";
+        case FST_DEV_ANCESTOR_OVERFLOW: return "a block has more unique ancestors than max_ancestors";
+        case FST_DEV_INDEX_RANGE: return "metadata index outside the K/V rows";
+        default: return "unknown status";
+    }
+}
+
+size_t fst_packed_meta_bytes(int n_blocks, int block_m, int max_ancestors) {
+    if (n_blocks <= 0 || block_m <= 0 || max_ancestors <= 0) return 0;
+    return packed_layout(n_blocks, block_m, max_ancestors).total;
+}
+
+int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m, int max_ancestors,
+                   int64_t *ancestor_idx, uint8_t *ancestor_mask, int64_t *leaf_idx, void *packed,
+                   size_t packed_tree_stride, int32_t *status, void *stream) {
+    if (!parent || n_trees <= 0 || n_nodes <= 0 || block_m <= 0 || max_ancestors <= 0)
+        return FST_ERR_INVALID_ARG;
+    if (block_m > 1024 || n_nodes > 262144 || n_trees > 65535 || max_ancestors > 65536)
+        return FST_ERR_TOO_LARGE;
+    if (size_t(block_m) * ((max_ancestors + 31) / 32) * 4 > 64 * 1024) return FST_ERR_TOO_LARGE;
+    const int nb = (n_nodes + block_m - 1) / block_m;
+    if (packed) {
+        if (!aligned16(packed) || (packed_tree_stride & 15)) return FST_ERR_ALIGNMENT;
+        if (n_trees > 1 && packed_tree_stride < packed_layout(nb, block_m, max_ancestors).total)
+            return FST_ERR_INVALID_ARG;
+    }
+    if ((max_ancestors & 3) == 0 && ancestor_mask && (reinterpret_cast<uintptr_t>(ancestor_mask) & 3))
+        return FST_ERR_ALIGNMENT;
+    return cuda_status(launch_precompute(parent, n_trees, n_nodes, block_m, max_ancestors,
+                                         ancestor_idx, ancestor_mask, leaf_idx, packed,
+                                         packed_tree_stride, status,
+                                         static_cast<cudaStream_t>(stream)));
+}
+
+int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                      const int64_t *leaf_idx, int n_trees, int n_blocks, int block_m,
+                      int max_ancestors, int64_t index_base, void *packed,
+                      size_t packed_tree_stride, int32_t *status, void *stream) {
+    if (!ancestor_idx || !ancestor_mask || !leaf_idx || !packed || n_trees <= 0 || n_blocks <= 0 ||
+        block_m <= 0 || max_ancestors <= 0)
+        return FST_ERR_INVALID_ARG;
+    if (n_trees > 65535 || max_ancestors > 65536) return FST_ERR_TOO_LARGE;
+    if (!aligned16(packed) || (packed_tree_stride & 15)) return FST_ERR_ALIGNMENT;
+    if (n_trees > 1 && packed_tree_stride < packed_layout(n_blocks, block_m, max_ancestors).total)
+        return FST_ERR_INVALID_ARG;
+    return cuda_status(launch_pack(ancestor_idx, ancestor_mask, leaf_idx, n_trees, n_blocks, block_m,
+                                   max_ancestors, index_base, packed, packed_tree_stride, status,
+                                   static_cast<cudaStream_t>(stream)));
+}
+
+int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse,
+                      const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
+                      int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                      int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                      int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                      int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
+                      int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
+                      void *stream) {
+    if (!q || !k || !v || !o || !packed || Z <= 0 || H <= 0 || n_q <= 0 || n_kv < n_q ||
+        block_m <= 0 || max_ancestors <= 0)
+        return FST_ERR_INVALID_ARG;
+    if (dtype != FST_F16 && dtype != FST_BF16 && dtype != FST_F32) return FST_ERR_INVALID_ARG;
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128)
+        return FST_ERR_UNSUPPORTED;                       // the reference's set, fstattention.py:157
+    if (H > 65535 || Z > 65535) return FST_ERR_TOO_LARGE;
+    if (!aligned16(packed) || (meta_tree_stride & 15)) return FST_ERR_ALIGNMENT;
+
+    AttnArgs a;
+    a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse;
+    a.packed = static_cast<const unsigned char *>(packed);
+    a.meta_stride = meta_tree_stride;
+    a.Z = Z; a.H = H; a.n_q = n_q; a.n_kv = n_kv; a.D = head_dim; a.prefix = n_kv - n_q;
+    a.qs_z = q_stride_z; a.qs_h = q_stride_h; a.qs_n = q_stride_n;
+    a.ks_z = k_stride_z; a.ks_h = k_stride_h; a.ks_n = k_stride_n;
+    a.vs_z = v_stride_z; a.vs_h = v_stride_h; a.vs_n = v_stride_n;
+    a.os_z = o_stride_z; a.os_h = o_stride_h; a.os_n = o_stride_n;
+    a.bm = block_m; a.ma = max_ancestors; a.nb = (n_q + block_m - 1) / block_m;
+    a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // the tensor-core kernel moves 16-byte pieces: every row must start on a 16-byte boundary
+    const int es = elem_size(dtype);
+    const int64_t strides[] = {q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                               v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n};
+    bool rows_aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o);
+    for (int64_t s : strides)
+        if ((s * es) & 15) rows_aligned = false;
+
+    int choice = kernel;
+    if (choice == FST_KERNEL_AUTO)
+        choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_MMA_T64
+                                                                    : FST_KERNEL_SIMT;
+    if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
+    if (choice != FST_KERNEL_MMA_T64 && choice != FST_KERNEL_MMA_T32) return FST_ERR_INVALID_ARG;
+    if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
+    if (!rows_aligned) return FST_ERR_ALIGNMENT;
+    return cuda_status(launch_attention_mma(a, dtype, choice == FST_KERNEL_MMA_T64 ? 64 : 32, st));
+}
+
+size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m, int max_ancestors) {
+    if (n_meta_trees <= 0 || n_q <= 0 || block_m <= 0 || max_ancestors <= 0) return 0;
+    const int nb = (n_q + block_m - 1) / block_m;
+    return size_t(n_meta_trees) * packed_layout(nb, block_m, max_ancestors).total;
+}
+
+int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, float *lse,
+                          const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                          const int64_t *leaf_idx, int n_meta_trees, int Z, int H, int n_q, int n_kv,
+                          int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                          int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                          int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                          int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
+                          int max_ancestors, float sm_scale, int dtype, int kernel, void *workspace,
+                          size_t workspace_bytes, int32_t *status, void *stream) {
+    if (!workspace) return FST_ERR_INVALID_ARG;
+    if (n_meta_trees != 1 && n_meta_trees != Z) return FST_ERR_INVALID_ARG;
+    if (n_q <= 0 || n_kv < n_q || block_m <= 0 || max_ancestors <= 0) return FST_ERR_INVALID_ARG;
+    const size_t need = fst_attention_ref_workspace_bytes(n_meta_trees, n_q, block_m, max_ancestors);
+    if (workspace_bytes < need) return FST_ERR_WORKSPACE;
+    const int nb = (n_q + block_m - 1) / block_m;
+    const size_t tree_bytes = packed_layout(nb, block_m, max_ancestors).total;
+    int rc = fst_pack_metadata(ancestor_idx, ancestor_mask, leaf_idx, n_meta_trees, nb, block_m,
+                               max_ancestors, int64_t(n_kv - n_q), workspace, tree_bytes, status,
+                               stream);
+    if (rc != FST_OK) return rc;
+    return fst_attention_fwd(q, k, v, o, lse, workspace, n_meta_trees == 1 ? 0 : tree_bytes, Z, H,
+                             n_q, n_kv, head_dim, q_stride_z, q_stride_h, q_stride_n, k_stride_z,
+                             k_stride_h, k_stride_n, v_stride_z, v_stride_h, v_stride_n, o_stride_z,
+                             o_stride_h, o_stride_n, block_m, max_ancestors, sm_scale, dtype, kernel,
+                             status, stream);
+}
+
+}  // extern "C"

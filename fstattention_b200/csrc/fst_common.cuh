@@ -1,0 +1,70 @@
+// Shared declarations for the fstattn_b200 kernels: packed-metadata layout, status record,
+// small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/fstattn_b200.h"
+
+namespace fst {
+
+// Offsets (bytes) of the four arrays inside one packed-metadata blob.
+struct PackedLayout {
+    int nb, bm, ma, maw, lw;
+    size_t off_count, off_idx, off_mask, off_leaf, total;
+};
+
+__host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
+
+__host__ __device__ inline PackedLayout packed_layout(int nb, int bm, int ma) {
+    PackedLayout L;
+    L.nb = nb; L.bm = bm; L.ma = ma;
+    L.maw = (ma + 31) / 32;
+    L.lw = (bm + 31) / 32;
+    L.off_count = 0;
+    L.off_idx = align16(size_t(nb) * 4);
+    L.off_mask = L.off_idx + align16(size_t(nb) * ma * 4);
+    L.off_leaf = L.off_mask + align16(size_t(nb) * bm * L.maw * 4);
+    L.total = L.off_leaf + align16(size_t(nb) * L.lw * 4);
+    return L;
+}
+
+// First error wins; later ones are dropped.
+__device__ inline void report(int32_t *status, int code, int where, int detail) {
+    if (status == nullptr) return;
+    if (atomicCAS(status, 0, code) == 0) {
+        status[1] = where;
+        status[2] = detail;
+    }
+}
+
+// Kernel launchers (defined in the .cu files, called from fst_api.cu)
+cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
+                              int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,
+                              void *packed, size_t packed_stride, int32_t *status,
+                              cudaStream_t stream);
+
+cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
+                        int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
+                        size_t packed_stride, int32_t *status, cudaStream_t stream);
+
+struct AttnArgs {
+    const void *q, *k, *v;
+    void *o;
+    float *lse;
+    const unsigned char *packed;
+    size_t meta_stride;
+    int Z, H, n_q, n_kv, D, prefix;
+    int64_t qs_z, qs_h, qs_n, ks_z, ks_h, ks_n, vs_z, vs_h, vs_n, os_z, os_h, os_n;
+    int bm, ma, nb;
+    float scale_log2;      // sm_scale * log2(e)
+    int32_t *status;
+};
+
+cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);
+// returns cudaErrorNotSupported when no tensor-core instantiation fits
+cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int tile_rows, cudaStream_t stream);
+
+}  // namespace fst

@@ -1,0 +1,305 @@
+// Tree precompute: parent array -> per-block ancestor list, row-by-ancestor mask, leaf list.
+//
+// Semantics follow the reference's create_fst_attention_kernel_inputs (utils.py:104-129):
+//   A_b   = ascending unique strict ancestors of the rows of block b          (utils.py:119)
+//   mask  = [row j][slot a] : A_b[a] is an ancestor of row j, or is row j     (utils.py:124-127)
+//   leaf  = rows of the block that are not in A_b, rows past the last node
+//           included                                                           (utils.py:121-122)
+// The reference gets there with unique / isin over a lineage matrix in Python loops; here one
+// CTA per (tree, block) marks ancestors in a shared-memory bitmap by walking parent links,
+// ranks the set bits with a popcount prefix scan (which yields the ascending order of
+// torch.unique without sorting) and walks each row's chain once more to set its mask bits.
+// Integer work only; the outputs are bit-identical to the reference's.
+//
+// Also here: the converter from reference-format metadata tensors to the packed form.
+
+#include "fst_common.cuh"
+
+namespace fst {
+
+constexpr int PRE_THREADS = 256;
+constexpr int PRE_WARPS = PRE_THREADS / 32;
+
+__global__ void __launch_bounds__(PRE_THREADS)
+precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, int ma, int par_cap,
+                  int64_t *__restrict__ anc_idx_all, uint8_t *__restrict__ anc_mask_all,
+                  int64_t *__restrict__ leaf_idx_all, unsigned char *__restrict__ packed_all,
+                  size_t packed_stride, int32_t *status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int b = blockIdx.x, tree = blockIdx.y, nb = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int row0 = b * bm;
+    const int row_end = row0 + bm;                       // may run past the last node
+    const int n_here = min(row_end, n_nodes);            // nodes that exist below row_end
+    const int W = (row_end + 31) >> 5;                   // bitmap words, phantom rows included
+    const int maw = (ma + 31) >> 5;
+
+    uint32_t *bitmap = reinterpret_cast<uint32_t *>(smem_raw);
+    int *rank = reinterpret_cast<int *>(bitmap + W);     // set bits in words below w
+    uint32_t *rowmask = reinterpret_cast<uint32_t *>(rank + W);
+    int *warp_tot = reinterpret_cast<int *>(rowmask + size_t(bm) * maw);
+    int *s_par = warp_tot + 40;
+
+    const int32_t *parent = parent_all + size_t(tree) * n_nodes;
+    const int cap = min(par_cap, n_here);
+    for (int i = tid; i < cap; i += PRE_THREADS) s_par[i] = parent[i];
+    for (int i = tid; i < W; i += PRE_THREADS) bitmap[i] = 0u;
+    for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
+    __syncthreads();
+
+    // parent of x; a malformed entry is reported and treated as a root, so every walk ends
+    auto par = [&](int x) -> int {
+        int p = x < cap ? s_par[x] : __ldg(parent + x);
+        if (p >= x || p < -1) {
+            report(status, FST_DEV_MALFORMED_TREE, x, p);
+            p = -1;
+        }
+        return p;
+    };
+
+    // 1. mark every strict ancestor of the block's rows.  A walker that finds a bit already set
+    //    stops: whoever set it keeps climbing, so everything above is (or will be) marked.
+    for (int j = tid; j < bm; j += PRE_THREADS) {
+        const int k = row0 + j;
+        if (k < n_nodes) {
+            int a = par(k);
+            while (a >= 0) {
+                const uint32_t bit = 1u << (a & 31);
+                const uint32_t old = atomicOr(&bitmap[a >> 5], bit);
+                if (old & bit) break;
+                a = par(a);
+            }
+        }
+    }
+    __syncthreads();
+
+    // 2. exclusive popcount scan over the bitmap words -> rank[w]
+    const int per = (W + PRE_THREADS - 1) / PRE_THREADS;
+    const int w0 = min(W, tid * per), w1 = min(W, w0 + per);
+    int mine = 0;
+    for (int w = w0; w < w1; ++w) mine += __popc(bitmap[w]);
+    int inc = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    if (lane == 31) warp_tot[wid] = inc;
+    __syncthreads();
+    if (wid == 0) {
+        const int v = lane < PRE_WARPS ? warp_tot[lane] : 0;
+        int iv = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, iv, o);
+            if (lane >= o) iv += u;
+        }
+        warp_tot[lane] = iv - v;
+        if (lane == 31) warp_tot[32] = iv;
+    }
+    __syncthreads();
+    {
+        int base = warp_tot[wid] + inc - mine;
+        for (int w = w0; w < w1; ++w) {
+            rank[w] = base;
+            base += __popc(bitmap[w]);
+        }
+    }
+    const int n_anc = warp_tot[32];
+    const int n_keep = min(n_anc, ma);
+    if (n_anc > ma && tid == 0) report(status, FST_DEV_ANCESTOR_OVERFLOW, tree * 65536 + b, n_anc);
+    __syncthreads();
+
+    const PackedLayout L = packed_layout(nb, bm, ma);
+    unsigned char *blob = packed_all ? packed_all + size_t(tree) * packed_stride : nullptr;
+    int32_t *p_count = blob ? reinterpret_cast<int32_t *>(blob + L.off_count) : nullptr;
+    int32_t *p_idx = blob ? reinterpret_cast<int32_t *>(blob + L.off_idx) + size_t(b) * ma : nullptr;
+    uint32_t *p_mask = blob ? reinterpret_cast<uint32_t *>(blob + L.off_mask) + size_t(b) * bm * maw
+                            : nullptr;
+    uint32_t *p_leaf = blob ? reinterpret_cast<uint32_t *>(blob + L.off_leaf) + size_t(b) * L.lw
+                            : nullptr;
+    const size_t blk = size_t(tree) * nb + b;
+    int64_t *o_idx = anc_idx_all ? anc_idx_all + blk * ma : nullptr;
+    uint8_t *o_mask = anc_mask_all ? anc_mask_all + blk * size_t(bm) * ma : nullptr;
+    int64_t *o_leaf = leaf_idx_all ? leaf_idx_all + blk * bm : nullptr;
+
+    // 3. ascending ancestor list: slot = rank of the bit
+    for (int w = tid; w < W; w += PRE_THREADS) {
+        uint32_t bits = bitmap[w];
+        int pos = rank[w];
+        while (bits) {
+            const int bit = __ffs(bits) - 1;
+            bits &= bits - 1;
+            if (pos < ma) {
+                const int node = w * 32 + bit;
+                if (p_idx) p_idx[pos] = node;
+                if (o_idx) o_idx[pos] = node;
+            }
+            ++pos;
+        }
+    }
+    for (int a = n_keep + tid; a < ma; a += PRE_THREADS) {
+        if (p_idx) p_idx[a] = -1;
+        if (o_idx) o_idx[a] = -1;
+    }
+    if (tid == 0 && p_count) p_count[b] = n_keep;
+
+    // 4. mask rows: the node itself (when it is somebody's ancestor in this block) and its chain
+    for (int j = tid; j < bm; j += PRE_THREADS) {
+        const int k = row0 + j;
+        if (k < n_nodes) {
+            int x = k;
+            while (x >= 0) {
+                const uint32_t word = bitmap[x >> 5];
+                const uint32_t bit = 1u << (x & 31);
+                if (word & bit) {
+                    const int pos = rank[x >> 5] + __popc(word & (bit - 1u));
+                    if (pos < ma) rowmask[j * maw + (pos >> 5)] |= 1u << (pos & 31);
+                }
+                x = par(x);
+            }
+        }
+    }
+    __syncthreads();
+
+    if (p_mask)
+        for (int i = tid; i < bm * maw; i += PRE_THREADS) p_mask[i] = rowmask[i];
+    if (o_mask) {
+        if ((ma & 3) == 0) {                             // four bool bytes per store
+            uint32_t *o32 = reinterpret_cast<uint32_t *>(o_mask);
+            const int n4 = bm * ma / 4;
+            for (int i = tid; i < n4; i += PRE_THREADS) {
+                const int e = i * 4, j = e / ma, a = e - j * ma;
+                const uint32_t nib = (rowmask[j * maw + (a >> 5)] >> (a & 31)) & 0xFu;
+                o32[i] = (nib & 1u) | ((nib & 2u) << 7) | ((nib & 4u) << 14) | ((nib & 8u) << 21);
+            }
+        } else {
+            for (int i = tid; i < bm * ma; i += PRE_THREADS) {
+                const int j = i / ma, a = i - j * ma;
+                o_mask[i] = (rowmask[j * maw + (a >> 5)] >> (a & 31)) & 1u;
+            }
+        }
+    }
+
+    // 5. leaves: block rows that are not in the ancestor set (rows past the last node too)
+    for (int j0 = 0; j0 < bm; j0 += PRE_THREADS) {
+        const int j = j0 + tid, k = row0 + j;
+        const bool leaf = j < bm && !((bitmap[k >> 5] >> (k & 31)) & 1u);
+        if (j < bm && o_leaf) o_leaf[j] = leaf ? int64_t(k) : int64_t(-1);
+        const uint32_t word = __ballot_sync(0xffffffffu, leaf);
+        if (lane == 0 && (j0 + wid * 32) < bm && p_leaf) p_leaf[(j0 >> 5) + wid] = word;
+    }
+}
+
+// -------------------------------------------------------------------------------------------
+// reference-format tensors -> packed blob
+// -------------------------------------------------------------------------------------------
+constexpr int PACK_THREADS = 128;
+
+__global__ void __launch_bounds__(PACK_THREADS)
+pack_kernel(const int64_t *__restrict__ anc_idx_all, const uint8_t *__restrict__ anc_mask_all,
+            const int64_t *__restrict__ leaf_idx_all, int bm, int ma, int64_t index_base,
+            unsigned char *__restrict__ packed_all, size_t packed_stride, int32_t *status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int b = blockIdx.x, tree = blockIdx.y, nb = gridDim.x;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int maw = (ma + 31) >> 5;
+    uint32_t *valid = reinterpret_cast<uint32_t *>(smem_raw);      // [maw]
+    __shared__ int s_count;
+    if (tid == 0) s_count = 0;
+    for (int i = tid; i < maw; i += PACK_THREADS) valid[i] = 0u;
+    __syncthreads();
+
+    const PackedLayout L = packed_layout(nb, bm, ma);
+    unsigned char *blob = packed_all + size_t(tree) * packed_stride;
+    int32_t *p_count = reinterpret_cast<int32_t *>(blob + L.off_count);
+    int32_t *p_idx = reinterpret_cast<int32_t *>(blob + L.off_idx) + size_t(b) * ma;
+    uint32_t *p_mask = reinterpret_cast<uint32_t *>(blob + L.off_mask) + size_t(b) * bm * maw;
+    uint32_t *p_leaf = reinterpret_cast<uint32_t *>(blob + L.off_leaf) + size_t(b) * L.lw;
+    const size_t blk = size_t(tree) * nb + b;
+    const int64_t *g_idx = anc_idx_all + blk * ma;
+    const uint8_t *g_mask = anc_mask_all + blk * size_t(bm) * ma;
+    const int64_t *g_leaf = leaf_idx_all + blk * bm;
+
+    for (int a = tid; a < ma; a += PACK_THREADS) {
+        const int64_t v = g_idx[a];
+        const int64_t rel = v - index_base;
+        const bool ok = v >= 0 && rel >= 0;
+        int32_t out = -1;
+        if (ok) {
+            if (rel > 0x7fffffffLL) {
+                report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, a);
+            } else {
+                out = int32_t(rel);
+                atomicOr(&valid[a >> 5], 1u << (a & 31));
+                atomicMax(&s_count, a + 1);
+            }
+        }
+        p_idx[a] = out;
+    }
+    __syncthreads();
+    if (tid == 0) p_count[b] = s_count;
+
+    for (int i = tid; i < bm * maw; i += PACK_THREADS) {
+        const int j = i / maw, w = i - j * maw;
+        const uint8_t *src = g_mask + size_t(j) * ma + w * 32;
+        const int n = min(32, ma - w * 32);
+        uint32_t word = 0u;
+        for (int a = 0; a < n; ++a) word |= (src[a] ? 1u : 0u) << a;
+        p_mask[i] = word & valid[w];
+    }
+
+    for (int j0 = 0; j0 < bm; j0 += PACK_THREADS) {
+        const int j = j0 + tid;
+        bool leaf = false;
+        if (j < bm) {
+            const int64_t v = g_leaf[j];
+            leaf = v >= 0 && v >= index_base;
+            if (leaf && v - index_base != int64_t(b) * bm + j)
+                report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, -1 - j);
+        }
+        const uint32_t word = __ballot_sync(0xffffffffu, leaf);
+        if (lane == 0 && (j0 + wid * 32) < bm) p_leaf[(j0 >> 5) + wid] = word;
+    }
+}
+
+static size_t g_pre_smem_set = 48 * 1024;
+
+cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
+                              int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,
+                              void *packed, size_t packed_stride, int32_t *status,
+                              cudaStream_t stream) {
+    const int nb = (n_nodes + bm - 1) / bm;
+    const int maw = (ma + 31) / 32;
+    const size_t W = (size_t(nb) * bm + 31) / 32;
+    const size_t fixed = (2 * W + size_t(bm) * maw + 40) * 4;
+    const size_t budget = 200 * 1024;
+    if (fixed + 1024 > budget) return cudaErrorInvalidValue;
+    const size_t cap = (budget - fixed) / 4;
+    const int par_cap = int(cap < size_t(n_nodes) ? cap : size_t(n_nodes));
+    const size_t smem = fixed + size_t(par_cap) * 4;
+    if (smem > g_pre_smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(precompute_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        g_pre_smem_set = smem;
+    }
+    dim3 grid(nb, n_trees);
+    precompute_kernel<<<grid, PRE_THREADS, smem, stream>>>(
+        parent, n_nodes, bm, ma, par_cap, anc_idx, anc_mask, leaf_idx,
+        static_cast<unsigned char *>(packed), packed_stride, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
+                        int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
+                        size_t packed_stride, int32_t *status, cudaStream_t stream) {
+    const int maw = (ma + 31) / 32;
+    dim3 grid(nb, n_trees);
+    pack_kernel<<<grid, PACK_THREADS, size_t(maw) * 4, stream>>>(
+        anc_idx, anc_mask, leaf_idx, bm, ma, index_base, static_cast<unsigned char *>(packed),
+        packed_stride, status);
+    return cudaGetLastError();
+}
+
+}  // namespace fst

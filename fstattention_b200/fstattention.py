@@ -1,0 +1,127 @@
+"""Attention entry point: the reference's ``fst_attention`` on the sm_100a kernels.
+
+Same positional signature as fstattention.py:153 of the reference::
+
+    o = fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale,
+                      BLOCK_M=128, MAX_ANCESTORS=64)
+
+``q`` is ``[Z, H, N, D]``, ``k``/``v`` are ``[Z, H, P + N, D]`` where the first ``P`` rows are a
+prefix every query attends to.  The launch is asynchronous on torch's current stream.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .utils import TreeMetadata, metadata_of
+
+_DTYPES = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16,
+           torch.float32: _lib.DTYPE_F32}
+_status = {}
+
+
+def _status_record(device) -> torch.Tensor:
+    rec = _status.get(device)
+    if rec is None:
+        rec = _status[device] = torch.zeros(_lib.STATUS_WORDS, dtype=torch.int32, device=device)
+    return rec
+
+
+def last_status(device=None) -> int:
+    """Device-side status code recorded by attention launches on ``device`` (synchronises)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    rec = _status.get(device)
+    return 0 if rec is None else int(rec[0].item())
+
+
+def _strides(t):
+    if t.stride(3) != 1:
+        raise ValueError("the head dimension must be contiguous")
+    return [t.stride(0), t.stride(1), t.stride(2)]
+
+
+def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_scale=None,
+                  BLOCK_M=128, MAX_ANCESTORS=64, *, out: Optional[torch.Tensor] = None,
+                  return_lse: bool = False, kernel: str = "auto"):
+    """Fused sparse tree attention forward.
+
+    ``ancestor_idx, ancestor_mask, leaf_idx`` are the tensors returned by
+    ``create_fst_attention_kernel_inputs`` (from this package, or the reference's moved to the
+    GPU) built with ``block_m=BLOCK_M`` and ``max_ancestors=MAX_ANCESTORS``; index tensors hold
+    absolute K/V rows, i.e. the caller adds the prefix length as fstattention.py:211-212 does.
+    Alternatively pass a ``TreeMetadata`` as ``ancestor_idx`` and leave the other two ``None``;
+    its block size and ancestor bound are used.  Metadata with a leading tree dimension of size
+    ``Z`` gives every batch element its own tree.
+
+    Asserts like the reference (fstattention.py:155-157): equal head dims, in {16, 32, 64, 128}.
+    """
+    if sm_scale is None:
+        raise TypeError("sm_scale is required")
+    Lq, Lk, Lv = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert Lq == Lk and Lk == Lv
+    assert Lk in {16, 32, 64, 128}
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("fst_attention runs on CUDA tensors only; there is no CPU path")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one dtype out of float16, bfloat16, float32")
+    Z, H, n_q, D = q.shape
+    n_kv = k.shape[2]
+    if k.shape != (Z, H, n_kv, D) or v.shape != k.shape or n_kv < n_q:
+        raise ValueError("k and v must be [Z, H, P + N, D] with P >= 0")
+    o = torch.empty_like(q) if out is None else out
+    if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
+        raise ValueError("out must match q")
+    lse = torch.empty((Z * H, n_q), device=q.device, dtype=torch.float32) if return_lse else None
+
+    lib = _lib.lib()
+    dev = q.device
+    status = _status_record(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    kern = _lib.KERNELS[kernel]
+    common_shape = [Z, H, n_q, n_kv, D] + _strides(q) + _strides(k) + _strides(v) + _strides(o)
+
+    meta = ancestor_idx if isinstance(ancestor_idx, TreeMetadata) else \
+        metadata_of(ancestor_idx, ancestor_mask, leaf_idx)
+    with torch.cuda.device(dev):
+        if meta is not None:
+            if meta.n_trees not in (1, Z):
+                raise ValueError("metadata must describe one tree or one tree per batch element")
+            if isinstance(ancestor_idx, TreeMetadata):
+                BLOCK_M, MAX_ANCESTORS = meta.block_m, meta.max_ancestors
+            elif (meta.block_m, meta.max_ancestors) != (BLOCK_M, MAX_ANCESTORS):
+                raise ValueError("BLOCK_M / MAX_ANCESTORS differ from the ones the metadata was built with")
+            if meta.n_blocks != -(-n_q // BLOCK_M):
+                raise ValueError("metadata block count does not match q")
+            rc = lib.fst_attention_fwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                lse.data_ptr() if lse is not None else None,
+                meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0,
+                *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern,
+                status.data_ptr(), stream)
+            _lib.check(rc, "fst_attention_fwd")
+        else:
+            ai, am, li = ancestor_idx, ancestor_mask, leaf_idx
+            if am is None or li is None:
+                raise TypeError("ancestor_mask and leaf_idx are required with plain tensors")
+            if not (ai.is_cuda and am.is_cuda and li.is_cuda):
+                raise RuntimeError("metadata tensors must be on the GPU (call .to('cuda') as the reference does)")
+            nb = -(-n_q // BLOCK_M)
+            n_meta = ai.shape[0] if ai.dim() == 3 else 1
+            if tuple(ai.shape[-2:]) != (nb, MAX_ANCESTORS) or tuple(am.shape[-3:]) != (nb, BLOCK_M, MAX_ANCESTORS) \
+                    or tuple(li.shape[-2:]) != (nb, BLOCK_M):
+                raise ValueError("metadata shapes do not match BLOCK_M / MAX_ANCESTORS / q")
+            if ai.dtype != torch.long or li.dtype != torch.long or am.dtype not in (torch.bool, torch.uint8):
+                raise TypeError("metadata dtypes must be int64 / bool / int64")
+            ai, am, li = ai.contiguous(), am.contiguous(), li.contiguous()
+            ws_bytes = int(lib.fst_attention_ref_workspace_bytes(n_meta, n_q, BLOCK_M, MAX_ANCESTORS))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            rc = lib.fst_attention_fwd_ref(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                lse.data_ptr() if lse is not None else None,
+                ai.data_ptr(), am.data_ptr(), li.data_ptr(), n_meta,
+                *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern,
+                ws.data_ptr(), ws_bytes, status.data_ptr(), stream)
+            _lib.check(rc, "fst_attention_fwd_ref")
+    return (o, lse) if return_lse else o

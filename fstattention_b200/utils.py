@@ -1,0 +1,198 @@
+"""Tree precompute: the reference's ``utils.py`` surface on top of the CUDA precompute kernel.
+
+``create_fst_attention_kernel_inputs`` keeps the reference's name, arguments, return order,
+dtypes and shapes (utils.py:104-129 of the reference) and raises ``RuntimeError`` where the
+reference does (more unique ancestors in a block than ``max_ancestors``, utils.py:120), but the
+work is done by one kernel launch on the GPU and the tensors it returns live there.
+``build_tree_metadata`` is the front door for callers that hold a parent array, which is what a
+decoder that rebuilds its tree every step has.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Union
+
+import torch
+
+from . import _lib
+
+TreeLike = Union[torch.Tensor, Sequence[int], Sequence[Sequence[int]]]
+
+
+class TreeMetadata:
+    """Block metadata of one tree or a batch of trees, resident on one GPU.
+
+    Unpacks like the reference's return value: ``ancestor_idx, ancestor_mask, leaf_idx = meta``
+    (int64 / bool / int64; a leading tree dimension is present only for a batch of trees).
+    ``packed`` is the bit-packed form the attention kernels read; ``fst_attention`` accepts the
+    object itself in place of the three tensors.
+    """
+
+    def __init__(self, n_trees, n_nodes, block_m, max_ancestors, packed, tree_stride, status,
+                 ancestor_idx=None, ancestor_mask=None, leaf_idx=None, batched=False):
+        self.n_trees, self.n_nodes = n_trees, n_nodes
+        self.block_m, self.max_ancestors = block_m, max_ancestors
+        self.n_blocks = math.ceil(n_nodes / block_m)
+        self.packed, self.tree_stride, self.status = packed, tree_stride, status
+        self.ancestor_idx, self.ancestor_mask, self.leaf_idx = ancestor_idx, ancestor_mask, leaf_idx
+        self.batched = batched
+        self._versions = self._current_versions()
+
+    def _current_versions(self):
+        return tuple(t._version if t is not None else -1
+                     for t in (self.ancestor_idx, self.ancestor_mask, self.leaf_idx))
+
+    def tensors_untouched(self) -> bool:
+        """True while nobody has modified the three reference-format tensors in place."""
+        return self._versions == self._current_versions()
+
+    def __iter__(self):
+        if self.ancestor_idx is None:
+            raise RuntimeError("metadata was built with reference_format=False")
+        return iter((self.ancestor_idx, self.ancestor_mask, self.leaf_idx))
+
+    def check(self) -> "TreeMetadata":
+        """Read the device status record (synchronises) and raise on a recorded problem."""
+        code, where, detail, _ = self.status.tolist()
+        if code == _lib.DEV_ANCESTOR_OVERFLOW:
+            raise RuntimeError(
+                f"block {where % 65536} of tree {where // 65536} has {detail} unique ancestors, "
+                f"more than max_ancestors={self.max_ancestors}")
+        if code == _lib.DEV_MALFORMED_TREE:
+            raise ValueError(f"malformed tree: parent[{where}]={detail} must be -1 or an earlier node")
+        if code != 0:
+            raise RuntimeError(_lib.status_string(code))
+        return self
+
+    @property
+    def device(self):
+        return self.packed.device
+
+
+# The three tensors handed out by the precompute remember the metadata they came from, so that
+# fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, ...) can skip re-packing them.
+_ORIGIN_ATTR = "_fst_tree_metadata"
+
+
+def metadata_of(ancestor_idx, ancestor_mask, leaf_idx) -> Optional[TreeMetadata]:
+    meta = getattr(ancestor_idx, _ORIGIN_ATTR, None)
+    if (meta is not None and meta.ancestor_idx is ancestor_idx and meta.ancestor_mask is ancestor_mask
+            and meta.leaf_idx is leaf_idx and meta.tensors_untouched()):
+        return meta
+    return None
+
+
+def _as_parent_tensor(parent: TreeLike, device) -> torch.Tensor:
+    if not torch.is_tensor(parent):
+        parent = torch.tensor(parent, dtype=torch.int32)
+    if parent.dim() not in (1, 2) or parent.numel() == 0:
+        raise ValueError("parent must be a non-empty [N] or [T, N] array")
+    return parent.to(device=device, dtype=torch.int32, non_blocking=True).contiguous()
+
+
+def packed_meta_bytes(n_blocks: int, block_m: int, max_ancestors: int) -> int:
+    return int(_lib.lib().fst_packed_meta_bytes(n_blocks, block_m, max_ancestors))
+
+
+def build_tree_metadata(parent: TreeLike, block_m: int = 64, max_ancestors: int = 32, *,
+                        reference_format: bool = True, check: bool = True,
+                        device: Union[str, torch.device, None] = None,
+                        out: Optional[TreeMetadata] = None) -> TreeMetadata:
+    """Parent array(s) -> block metadata, with one kernel launch on the current stream.
+
+    ``parent`` is ``[N]`` (one tree) or ``[T, N]`` (T independent trees of N nodes); entries are
+    -1 for roots and otherwise the index of an earlier node.  ``reference_format=False`` skips
+    the int64/bool tensors and writes only the packed form.  ``check=False`` skips reading the
+    status record, which avoids a device synchronisation; call ``.check()`` later.  ``out``
+    reuses the buffers of an earlier result of the same shape (nothing is allocated then).
+    """
+    if device is None:
+        device = parent.device if torch.is_tensor(parent) and parent.is_cuda else "cuda"
+    par = _as_parent_tensor(parent, device)
+    batched = par.dim() == 2
+    n_trees, n_nodes = (par.shape if batched else (1, par.shape[0]))
+    nb = math.ceil(n_nodes / block_m)
+    lib = _lib.lib()
+    dev = par.device
+    if out is not None:
+        if (out.n_trees, out.n_nodes, out.block_m, out.max_ancestors) != (n_trees, n_nodes, block_m, max_ancestors):
+            raise ValueError("out= metadata has a different shape")
+        meta = out
+        meta.status.zero_()
+    else:
+        stride = packed_meta_bytes(nb, block_m, max_ancestors)
+        if stride == 0:
+            raise ValueError("block_m and max_ancestors must be positive")
+        packed = torch.empty((n_trees, stride), dtype=torch.uint8, device=dev)
+        status = torch.zeros(_lib.STATUS_WORDS, dtype=torch.int32, device=dev)
+        ai = am = li = None
+        if reference_format:
+            lead = (n_trees,) if batched else ()
+            ai = torch.empty(lead + (nb, max_ancestors), dtype=torch.long, device=dev)
+            am = torch.empty(lead + (nb, block_m, max_ancestors), dtype=torch.bool, device=dev)
+            li = torch.empty(lead + (nb, block_m), dtype=torch.long, device=dev)
+        meta = TreeMetadata(n_trees, n_nodes, block_m, max_ancestors, packed, stride, status,
+                            ai, am, li, batched)
+        if reference_format:
+            setattr(ai, _ORIGIN_ATTR, meta)
+    with torch.cuda.device(dev):
+        rc = lib.fst_precompute(
+            par.data_ptr(), n_trees, n_nodes, block_m, max_ancestors,
+            meta.ancestor_idx.data_ptr() if meta.ancestor_idx is not None else None,
+            meta.ancestor_mask.data_ptr() if meta.ancestor_mask is not None else None,
+            meta.leaf_idx.data_ptr() if meta.leaf_idx is not None else None,
+            meta.packed.data_ptr(), meta.tree_stride, meta.status.data_ptr(),
+            torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "fst_precompute")
+    meta._versions = meta._current_versions()
+    if check:
+        meta.check()
+    return meta
+
+
+def parent_from_lineage(lineage: torch.Tensor, level_lookup: torch.Tensor) -> torch.Tensor:
+    """parent[k] = lineage[k, level_lookup[k] - 1], -1 for level-0 nodes (utils.py:42-44)."""
+    lvl = level_lookup.to(lineage.device).long()
+    col = (lvl - 1).clamp_min(0).unsqueeze(1)
+    par = lineage.gather(1, col).squeeze(1)
+    return torch.where(lvl > 0, par, torch.full_like(par, -1))
+
+
+def create_fst_attention_kernel_inputs(lineage: torch.Tensor, level_lookup: torch.Tensor,
+                                       block_m: int = 64, max_ancestors: int = 32,
+                                       mutate_lineage: bool = True):
+    """Drop-in for the reference function of the same name (utils.py:104-129).
+
+    Returns ``ancestor_idx [nb, max_ancestors]`` (int64), ``ancestor_mask [nb, block_m,
+    max_ancestors]`` (bool) and ``leaf_idx [nb, block_m]`` (int64) with the reference's values,
+    as CUDA tensors.  Raises RuntimeError when a block has more than ``max_ancestors`` unique
+    ancestors.  Like the reference (utils.py:124-125) it writes every node into its own lineage
+    row as a side effect; pass ``mutate_lineage=False`` to leave ``lineage`` alone.
+    """
+    parent = parent_from_lineage(lineage, level_lookup)
+    meta = build_tree_metadata(parent, block_m, max_ancestors, reference_format=True, check=True)
+    if mutate_lineage:
+        n = lineage.shape[0]
+        rows = torch.arange(n, device=lineage.device)
+        lineage[rows, level_lookup.to(lineage.device).long()] = rows
+    return meta.ancestor_idx, meta.ancestor_mask, meta.leaf_idx
+
+
+def lineage_from_parent(parent: Sequence[int]):
+    """Parent array -> (lineage, level_lookup) as the reference describes trees (utils.py:42-44).
+
+    Host-side adapter for callers that still want the reference's inputs; CPU tensors.
+    """
+    n = len(parent)
+    level = [0] * n
+    for i, p in enumerate(parent):
+        if p >= i or p < -1:
+            raise ValueError(f"parent[{i}]={p} must be -1 or an earlier node")
+        level[i] = 0 if p < 0 else level[p] + 1
+    width = max(level) + 1
+    lin = torch.full((n, width), -1, dtype=torch.long)
+    for i, p in enumerate(parent):
+        if p >= 0:
+            lin[i, : level[p]] = lin[p, : level[p]]
+            lin[i, level[p]] = p
+    return lin, torch.tensor(level, dtype=torch.long)

@@ -1,0 +1,157 @@
+/*
+ * fstattn_b200 - fused sparse tree attention for NVIDIA B200 (sm_100a), C ABI.
+ *
+ * Everything here is plain C: device pointers, sizes and a CUDA stream handle passed as
+ * void*.  No function allocates, frees or synchronises; each one enqueues its kernels on the
+ * given stream and returns a status code (0 = FST_OK) describing host-side argument checks.
+ * Problems that only the GPU can see (a malformed tree, too many ancestors in a block, an
+ * index out of range) are recorded in a caller-provided device status record
+ * (int32_t status[FST_STATUS_WORDS]) and never fault the device; the kernels keep going with
+ * the offending element ignored.  Clear the record once (cudaMemsetAsync) and read it back
+ * whenever a check is wanted.
+ *
+ * "Reference" below means the project this library is a drop-in for; paths are inside it.
+ */
+#ifndef FSTATTN_B200_H
+#define FSTATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FST_VERSION 100
+#define FST_STATUS_WORDS 4   /* status[0]=code, [1]=tree*65536+block or row, [2]=detail, [3]=spare */
+
+enum fst_status {
+    FST_OK = 0,
+    FST_ERR_INVALID_ARG = 1,       /* null pointer, non-positive size, unknown enum            */
+    FST_ERR_UNSUPPORTED = 2,       /* head_dim / dtype / block_m combination has no kernel      */
+    FST_ERR_ALIGNMENT = 3,         /* pointer or stride not 16-byte aligned                     */
+    FST_ERR_WORKSPACE = 4,         /* workspace too small                                       */
+    FST_ERR_CUDA = 5,              /* a CUDA runtime call failed (launch configuration)         */
+    FST_ERR_TOO_LARGE = 6,         /* size beyond a documented limit                            */
+    /* device-side codes, written to status[0] */
+    FST_DEV_MALFORMED_TREE = 16,   /* parent[i] >= i or < -1; status[1] = node                  */
+    FST_DEV_ANCESTOR_OVERFLOW = 17,/* a block has more unique ancestors than max_ancestors;     */
+                                   /* status[1] = tree*65536+block, status[2] = the count        */
+    FST_DEV_INDEX_RANGE = 18       /* a metadata index points outside the K/V rows              */
+};
+
+enum fst_dtype { FST_F16 = 0, FST_BF16 = 1, FST_F32 = 2 };
+
+/* Kernel choice for fst_attention_fwd*; FST_KERNEL_AUTO is what callers want. */
+enum fst_kernel {
+    FST_KERNEL_AUTO = 0,
+    FST_KERNEL_SIMT = 1,           /* fp32 arithmetic, any dtype / head_dim in {16,32,64,128}   */
+    FST_KERNEL_MMA_T64 = 2,        /* tensor-core kernel, 64-row K/V tiles                      */
+    FST_KERNEL_MMA_T32 = 3         /* tensor-core kernel, 32-row K/V tiles (more CTAs per SM)   */
+};
+
+int fst_version(void);
+const char *fst_status_string(int status);
+
+/*
+ * Packed block metadata, the form the attention kernels read.  For one tree with
+ * n_blocks = ceil(n_nodes / block_m) query blocks it is one blob of
+ * fst_packed_meta_bytes() bytes holding four arrays, each starting on a 16-byte boundary:
+ *   int32  count[n_blocks]                 unique ancestors of the block
+ *   int32  idx  [n_blocks][max_ancestors]  their node indices, ascending, -1 padded
+ *   uint32 mask [n_blocks][block_m][W]     W = ceil(max_ancestors/32); bit a of row j set when
+ *                                          row j attends to ancestor slot a
+ *   uint32 leaf [n_blocks][ceil(block_m/32)] bit j set when row j attends to itself through
+ *                                          the leaf path (it is not in the block's ancestor list)
+ * Indices are relative to the first tree row (the shared prefix is not counted).
+ * A batch of trees is an array of such blobs, meta_tree_stride bytes apart.
+ */
+size_t fst_packed_meta_bytes(int n_blocks, int block_m, int max_ancestors);
+
+/*
+ * Tree precompute on the GPU.  Replaces utils.py:104-129
+ * (create_fst_attention_kernel_inputs) of the reference, taking the tree as a parent array
+ * instead of lineage/level_lookup (utils.py:42-44): parent[t][i] in [-1, i), -1 for roots.
+ *
+ * For each of n_trees trees (parent arrays n_nodes apart) writes, when the pointer is not
+ * NULL:
+ *   ancestor_idx  int64 [n_trees][n_blocks][max_ancestors]           (-1 padded)
+ *   ancestor_mask uint8 [n_trees][n_blocks][block_m][max_ancestors]  (0/1, torch.bool layout)
+ *   leaf_idx      int64 [n_trees][n_blocks][block_m]                 (-1 where not a leaf)
+ *   packed        blobs as described above, packed_tree_stride bytes apart
+ * bit-identical to the reference, including leaf entries past the last node in a partial
+ * last block (utils.py:121-122).  Where the reference raises on more than max_ancestors
+ * ancestors (utils.py:120) this records FST_DEV_ANCESTOR_OVERFLOW and keeps the first
+ * max_ancestors.  Limits: 1 <= block_m <= 1024, n_nodes <= 262144.
+ */
+int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m,
+                   int max_ancestors, int64_t *ancestor_idx, uint8_t *ancestor_mask,
+                   int64_t *leaf_idx, void *packed, size_t packed_tree_stride,
+                   int32_t *status, void *stream);
+
+/*
+ * Convert reference-format metadata (the three tensors of utils.py:104-129, already on the
+ * device) into packed blobs.  index_base is subtracted from every index; entries below it
+ * are padding.  The reference's test shifts the index tensors by the prefix length,
+ * sentinels included (fstattention.py:211-212); with index_base = prefix length both the
+ * shifted sentinels and plain -1 read as padding here.
+ */
+int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                      const int64_t *leaf_idx, int n_trees, int n_blocks, int block_m,
+                      int max_ancestors, int64_t index_base, void *packed,
+                      size_t packed_tree_stride, int32_t *status, void *stream);
+
+/*
+ * Fused sparse tree attention, forward.  Replaces the kernel and launch of
+ * fstattention.py:21-181 (_fwd_kernel / fst_attention).
+ *
+ *   q, o : [Z][H][n_q][head_dim]      strides in elements, innermost dimension contiguous
+ *   k, v : [Z][H][n_kv][head_dim]     rows [0, prefix_len) are a prefix every query attends
+ *                                      to; tree node i lives in row prefix_len + i
+ *   lse  : optional float [Z][H][n_q], base-2 log-sum-exp of the scaled scores
+ *          (fstattention.py:140-141); NULL to skip
+ *   packed, meta_tree_stride : packed metadata; stride 0 shares one tree between all Z
+ *          (the reference's behaviour, fstattention.py:62-67), otherwise tree z is used for
+ *          batch element z
+ * The prefix length is n_kv - n_q, as in fstattention.py:163.  Block rows >= n_q are neither
+ * read nor written, so n_q need not be a multiple of block_m.
+ * dtype: FST_F16 / FST_BF16 (tensor cores, head_dim 64 or 128, block_m 16..128 multiple of
+ * 16) or any of the three with head_dim in {16,32,64,128} on the fp32 SIMT kernel.
+ */
+int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse,
+                      const void *packed, size_t meta_tree_stride,
+                      int Z, int H, int n_q, int n_kv, int head_dim,
+                      int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                      int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                      int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                      int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                      int block_m, int max_ancestors, float sm_scale, int dtype, int kernel,
+                      int32_t *status, void *stream);
+
+/*
+ * The same with reference-format metadata, i.e. exactly the arguments of the reference's
+ * fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale, BLOCK_M,
+ * MAX_ANCESTORS) (fstattention.py:153).  Index tensors hold absolute K/V rows
+ * (tree index + prefix length); n_meta_trees is 1 (shared) or Z.  workspace is scratch
+ * device memory of at least fst_attention_ref_workspace_bytes() bytes, 16-byte aligned, that
+ * the call fills with the packed form and the attention kernel then reads; it must stay
+ * untouched until the call has finished on the stream.
+ */
+size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m,
+                                         int max_ancestors);
+int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, float *lse,
+                          const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                          const int64_t *leaf_idx, int n_meta_trees,
+                          int Z, int H, int n_q, int n_kv, int head_dim,
+                          int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                          int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                          int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                          int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                          int block_m, int max_ancestors, float sm_scale, int dtype, int kernel,
+                          void *workspace, size_t workspace_bytes,
+                          int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSTATTN_B200_H */

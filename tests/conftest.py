@@ -43,3 +43,16 @@ def unpack_golden_metadata(case):
     li = torch.from_numpy(case["leaf_idx"].astype(np.int64))
     am = np.unpackbits(case["ancestor_mask_bits"], axis=2)[:, :, :ma].astype(bool)
     return ai, torch.from_numpy(am), li, bm, ma
+
+
+@pytest.fixture(scope="session")
+def built_lib():
+    """Path of the C-ABI library, built first when it is missing or stale and nvcc is here."""
+    from fstattention_b200 import build as fst_build
+    if not fst_build.up_to_date():
+        try:
+            fst_build.build()
+        except RuntimeError:
+            if not os.path.exists(fst_build.LIB):
+                raise
+    return fst_build.LIB

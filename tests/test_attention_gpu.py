@@ -1,0 +1,236 @@
+"""Tree attention kernels against the reference's outputs (golden) and the CPU oracle.
+
+Tolerances.  fp16/bf16 kernels are gated at max-abs 2e-3 (fp16) against the oracle formula
+evaluated on the same fp16 inputs in float32; against the oracle exactly as the reference
+writes it (fp16 scores and probabilities) the gate is 2e-3 plus that formula's own measured
+rounding error versus float64, because its noise alone exceeds 2e-3 at |out| ~ 4.  The
+reference's own test accepts 1e-2 (fstattention.py:228).  fp32 inputs: 2e-5.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import unpack_golden_metadata
+from helpers import chain_mean_values, make_qkv, oracle_attention
+from oracle import tree_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL_F16 = 2e-3
+TOL_BF16 = 1.6e-2          # bf16 has 8 fewer mantissa bits than fp16
+TOL_F32 = 2e-5
+
+
+@pytest.fixture(scope="module")
+def fst(built_lib):
+    import fstattention_b200
+    return fstattention_b200
+
+
+def kernels_for(dtype, d, bm):
+    ks = ["auto", "simt"]
+    if dtype in (torch.float16, torch.bfloat16) and d in (64, 128) and bm in (16, 32, 64, 128):
+        ks += ["mma_t64", "mma_t32"]
+    return ks
+
+
+def maxabs(a, b):
+    return (a.double() - b.double()).abs().max().item()
+
+
+def test_golden_cases_all_kernels(fst, attention_golden):
+    for name, case in attention_golden.items():
+        q, k, v = (torch.from_numpy(case[x]) for x in ("q", "k", "v"))
+        n, bm, ma, prefix = (int(case[x]) for x in ("n", "block_m", "max_ancestors", "prefix"))
+        scale = float(case["sm_scale"])
+        par = case["parent"].tolist()
+        meta = fst.build_tree_metadata(par, bm, ma)
+        dense = torch.from_numpy(case["out_dense"])[:, :, :n]
+        tri = torch.from_numpy(case["out_triton"])[:, :, :n]
+        exact32 = orc.tree_attention_reference(q, k, v, par, scale, bm, prefix, torch.float32)[:, :, :n]
+        exact64 = orc.tree_attention_reference(q, k, v, par, scale, bm, prefix, torch.float64)[:, :, :n]
+        noise = maxabs(dense, exact64)
+        tol = TOL_F32 if q.dtype == torch.float32 else TOL_F16
+        for kern in kernels_for(q.dtype, q.shape[-1], bm):
+            o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern)
+            o = o.cpu()[:, :, :n]
+            assert torch.isfinite(o).all(), (name, kern)
+            assert maxabs(o, exact32) <= tol, (name, kern, maxabs(o, exact32))
+            assert maxabs(o, dense) <= tol + noise, (name, kern, maxabs(o, dense), noise)
+            assert maxabs(o, tri) <= 1e-2, (name, kern)          # the reference test's own gate
+        assert fst.last_status() == 0
+
+
+def test_reference_call_sequence_with_prefix(fst, attention_golden):
+    """The reference test's calling convention verbatim: tensors shifted by the prefix length,
+    sentinels included (fstattention.py:211-212), then .to('cuda') and positional arguments."""
+    case = attention_golden["reftree_d5_prefix128"]
+    q, k, v = (torch.from_numpy(case[x]).cuda() for x in ("q", "k", "v"))
+    n, bm, ma, prefix = (int(case[x]) for x in ("n", "block_m", "max_ancestors", "prefix"))
+    ai, am, li = orc.block_metadata_from_parent(case["parent"].tolist(), bm, ma)
+    ai += prefix
+    li += prefix
+    o = fst.fst_attention(q, k, v, ai.to("cuda"), am.to("cuda"), li.to("cuda"), float(case["sm_scale"]),
+                          BLOCK_M=bm, MAX_ANCESTORS=ma)
+    exact = orc.tree_attention_reference(q.cpu(), k.cpu(), v.cpu(), case["parent"].tolist(),
+                                         float(case["sm_scale"]), bm, prefix, torch.float32)
+    assert maxabs(o.cpu()[:, :, :n], exact[:, :, :n]) <= TOL_F16
+    # and with this package's own precompute, shifted in place the same way
+    g_ai, g_am, g_li = fst.build_tree_metadata(case["parent"].tolist(), bm, ma)
+    g_ai += prefix
+    g_li += prefix
+    o2 = fst.fst_attention(q, k, v, g_ai, g_am, g_li, float(case["sm_scale"]), BLOCK_M=bm, MAX_ANCESTORS=ma)
+    assert torch.equal(o, o2)
+    assert fst.last_status() == 0
+
+
+WORKLOAD_CASES = [("binary31", 4, None), ("medusa256", 32, None), ("random1024", 8, 0),
+                  ("random1024", 4, 7), ("deep4096", 2, None)]
+
+
+@pytest.mark.parametrize("name,heads,step", WORKLOAD_CASES)
+def test_workloads_vs_oracle(fst, name, heads, step):
+    from fstattention_b200 import configs
+    w = configs.workload(name, step or 0)
+    dtype = {"fp16": torch.float16, "fp32": torch.float32}[w.dtype]
+    par = w.trees[0]
+    n = len(par)
+    q, k, v = make_qkv(1, heads, n, n, w.head_dim, dtype, seed=11)
+    meta = fst.build_tree_metadata(par, w.block_m, w.max_ancestors)
+    exact = oracle_attention(q, k, v, par, w.sm_scale, compute_dtype=torch.float32, head_chunk=2)
+    tol = TOL_F32 if dtype == torch.float32 else TOL_F16
+    for kern in kernels_for(dtype, w.head_dim, w.block_m):
+        o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
+        assert maxabs(o, exact) <= tol, (name, kern, maxabs(o, exact))
+    assert fst.last_status() == 0
+
+
+def test_forest_per_tree_metadata(fst):
+    from fstattention_b200 import configs
+    w = configs.workload("forest64")
+    trees = w.trees[:8]
+    q, k, v = make_qkv(8, 4, 256, 256, 128, torch.float16, seed=5)
+    meta = fst.build_tree_metadata(trees, w.block_m, w.max_ancestors)
+    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale).cpu()
+    for t in range(8):
+        exact = oracle_attention(q[t:t + 1], k[t:t + 1], v[t:t + 1], trees[t], w.sm_scale,
+                                 compute_dtype=torch.float32)
+        assert maxabs(o[t:t + 1], exact) <= TOL_F16, t
+    # reference-format tensors with a leading tree dimension give the same answer
+    ai, am, li = meta
+    ai2, am2, li2 = ai.clone(), am.clone(), li.clone()
+    o2 = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), ai2, am2, li2, w.sm_scale,
+                           BLOCK_M=w.block_m, MAX_ANCESTORS=w.max_ancestors).cpu()
+    assert torch.equal(o, o2)
+
+
+@pytest.mark.parametrize("name", ["medusa256", "random1024", "forest64", "deep4096"])
+def test_full_size_equal_scores_property(fst, name):
+    """Full BASELINE sizes.  With K = 0 every attended key gets the same weight, so each output
+    row must be the mean of V over the node and its ancestors - computable exactly in O(N)."""
+    from fstattention_b200 import configs
+    w = configs.workload(name)
+    T, n, H, D = len(w.trees), w.n_nodes, w.heads, w.head_dim
+    g = torch.Generator().manual_seed(3)
+    v = torch.randn((T, H, n, D), generator=g).half()
+    q = torch.randn((T, H, n, D), generator=g).half()
+    k = torch.zeros_like(v)
+    meta = fst.build_tree_metadata(w.trees if T > 1 else w.trees[0], w.block_m, w.max_ancestors)
+    for kern in ("mma_t64", "mma_t32"):
+        o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
+        for t in range(0, T, 9):
+            want = chain_mean_values(w.trees[t], v[t].double().numpy())
+            err = np.abs(o[t].double().numpy() - want).max()
+            assert err <= TOL_F16, (name, kern, t, err)
+    # rows sum to one: V = 1 gives exactly 1 whatever the scores are
+    k = torch.randn((T, H, n, D), generator=g).half()
+    o = fst.fst_attention(q.cuda(), k.cuda(), torch.ones_like(v).cuda(), meta, sm_scale=w.sm_scale).cpu()
+    assert (o.float() - 1).abs().max().item() <= 1e-3
+    assert fst.last_status() == 0
+
+
+def test_full_size_kernels_agree(fst):
+    """deep4096 at full head count: tensor-core kernels against the fp32 SIMT kernel."""
+    from fstattention_b200 import configs
+    w = configs.workload("deep4096")
+    q, k, v = (x.cuda() for x in make_qkv(1, w.heads, w.n_nodes, w.n_nodes, w.head_dim, torch.float16, 17))
+    meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors)
+    base = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel="simt")
+    for kern in ("mma_t64", "mma_t32"):
+        o = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel=kern)
+        assert maxabs(o, base) <= TOL_F16, kern
+
+
+@pytest.mark.parametrize("dtype,d,bm,prefix", [
+    (torch.float16, 128, 64, 64), (torch.float16, 128, 64, 200), (torch.float16, 64, 128, 37),
+    (torch.bfloat16, 128, 64, 0), (torch.bfloat16, 64, 32, 96), (torch.float16, 32, 64, 16),
+    (torch.float32, 16, 16, 5), (torch.float32, 128, 128, 130), (torch.float16, 128, 16, 0),
+])
+def test_shapes_dtypes_and_prefix(fst, dtype, d, bm, prefix):
+    from fstattention_b200 import configs
+    par = configs.random_window_tree(5, 300, 24)        # 300 rows: partial last block
+    n = len(par)
+    q, k, v = make_qkv(2, 3, n, prefix + n, d, dtype, seed=9)
+    ma = 128
+    meta = fst.build_tree_metadata(par, bm, ma)
+    scale = d ** -0.5
+    exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
+    tol = {torch.float16: TOL_F16, torch.bfloat16: TOL_BF16, torch.float32: TOL_F32}[dtype]
+    for kern in kernels_for(dtype, d, bm):
+        o, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern,
+                                   return_lse=True)
+        assert maxabs(o.cpu(), exact) <= tol, (kern, maxabs(o.cpu(), exact))
+        # base-2 log-sum-exp of the scaled scores (fstattention.py:140-141)
+        lin, _ = orc.lineage_from_parent(par)
+        mask = torch.cat((torch.ones((n, prefix)), orc.full_attention_mask(lin, 0)), dim=1)
+        s = torch.matmul(q.double(), k.double().transpose(2, 3)) * scale
+        s[:, :, mask == 0] = float("-inf")
+        want = torch.logsumexp(s, dim=-1) / np.log(2.0)
+        assert maxabs(lse.cpu().view(2, 3, n), want) <= (2e-2 if dtype == torch.bfloat16 else 2e-3), kern
+    assert fst.last_status() == 0
+
+
+def test_strided_inputs_and_out_argument(fst):
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D = 256, 4, 128
+    g = torch.Generator().manual_seed(2)
+    # [Z, N, H, D] storage viewed as [Z, H, N, D], as a projection layer would leave it
+    q, k, v = (torch.randn((2, n, H, D), generator=g).half().cuda().permute(0, 2, 1, 3) for _ in range(3))
+    meta = fst.build_tree_metadata(par, 64, 64)
+    out = torch.empty((2, n, H, D), dtype=torch.float16, device="cuda").permute(0, 2, 1, 3)
+    o = fst.fst_attention(q, k, v, meta, sm_scale=D ** -0.5, out=out)
+    assert o.data_ptr() == out.data_ptr()
+    exact = oracle_attention(q.cpu().contiguous(), k.cpu().contiguous(), v.cpu().contiguous(), par,
+                             D ** -0.5, compute_dtype=torch.float32)
+    assert maxabs(o.cpu(), exact) <= TOL_F16
+
+
+def test_padded_tensors_phantom_rows(fst):
+    """Tensors padded to a whole number of blocks, as the reference pads 2^k-4 trees to 2^k:
+    rows past the last node attend only to themselves and the real rows are unaffected."""
+    par = [-1] + [(i - 1) // 2 for i in range(1, 31)]
+    q, k, v = make_qkv(1, 2, 32, 32, 64, torch.float16, seed=4)
+    meta = fst.build_tree_metadata(par, 16, 16)
+    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=0.125).cpu()
+    exact = oracle_attention(q[:, :, :31], k[:, :, :31], v[:, :, :31], par, 0.125, compute_dtype=torch.float32)
+    assert maxabs(o[:, :, :31], exact) <= TOL_F16
+    assert maxabs(o[:, :, 31], v[:, :, 31]) <= 1e-3
+
+
+def test_argument_errors_are_python_errors(fst):
+    par = [-1, 0, 0, 1]
+    meta = fst.build_tree_metadata(par, 16, 16)
+    q = torch.randn(1, 1, 4, 64).half()
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        fst.fst_attention(q, q, q, meta, sm_scale=1.0)
+    qc = q.cuda()
+    with pytest.raises(AssertionError):
+        fst.fst_attention(qc[..., :24], qc[..., :24], qc[..., :24], meta, sm_scale=1.0)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        fst.fst_attention(qc.float(), qc.float(), qc.float(), meta, sm_scale=1.0, kernel="mma_t64")
+    odd = torch.randn(1, 1, 4, 72).half().cuda()[..., 4:68]           # rows start 8 bytes off
+    with pytest.raises(RuntimeError, match="aligned"):
+        fst.fst_attention(odd, odd, odd, meta, sm_scale=1.0, kernel="mma_t64")
+    fst.fst_attention(odd, odd, odd, meta, sm_scale=1.0, kernel="simt")   # the SIMT kernel takes it
+    torch.cuda.synchronize()

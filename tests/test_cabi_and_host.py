@@ -1,0 +1,85 @@
+"""CPU-only checks: the library loads and exports the header's symbols; host-side logic."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    header = open(os.path.join(ROOT, "include", "fstattn_b200.h")).read()
+    code = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(fst_[a-z_0-9]+)\s*\(", code))
+    assert len(declared) >= 8
+    lib = ctypes.CDLL(built_lib)
+    for name in declared:
+        assert hasattr(lib, name), name
+    from fstattention_b200 import _lib
+    assert set(_lib.EXPORTS) == declared
+
+
+def test_host_only_entry_points(built_lib):
+    from fstattention_b200 import _lib
+    lib = _lib.lib()
+    assert lib.fst_version() == 100
+    assert "max_ancestors" in _lib.status_string(17)
+    assert _lib.status_string(0) == "ok"
+    # layout: count | idx | mask | leaf, every part 16-byte aligned
+    assert lib.fst_packed_meta_bytes(4, 64, 64) == 16 + 4 * 64 * 4 + 4 * 64 * 2 * 4 + 32
+    assert lib.fst_packed_meta_bytes(0, 64, 64) == 0
+    assert lib.fst_attention_ref_workspace_bytes(2, 256, 64, 64) == 2 * lib.fst_packed_meta_bytes(4, 64, 64)
+    # argument checks happen before any CUDA call
+    assert lib.fst_precompute(None, 1, 4, 16, 16, None, None, None, None, 0, None, None) == 1
+    assert lib.fst_precompute(ctypes.c_void_p(256), 1, 1 << 20, 16, 16, None, None, None, None, 0, None, None) == 6
+
+
+def test_packed_layout_helper_agrees_with_library(built_lib):
+    from fstattention_b200 import _lib
+    from helpers import packed_offsets
+    lib = _lib.lib()
+    for nb, bm, ma in [(1, 16, 16), (4, 64, 64), (16, 64, 256), (64, 64, 128), (33, 128, 192), (3, 24, 40)]:
+        assert packed_offsets(nb, bm, ma)[3] == lib.fst_packed_meta_bytes(nb, bm, ma)
+
+
+def test_cpu_tensors_are_refused():
+    import fstattention_b200 as fst
+    q = torch.zeros(1, 1, 16, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fst.fst_attention(q, q, q, q.long(), q.bool(), q.long(), 1.0)
+    with pytest.raises(AssertionError):
+        fst.fst_attention(q[..., :48], q[..., :48], q[..., :48], None, None, None, 1.0)
+
+
+def test_lineage_adapters_round_trip(metadata_golden):
+    import fstattention_b200 as fst
+    from oracle import tree_oracle as orc
+    for name in ("binary31_bm16", "multiroot157_bm32", "reftree_d3_bm32", "medusa256_bm64"):
+        par = metadata_golden[name]["parent"].tolist()
+        lin, lvl = fst.lineage_from_parent(par)
+        o_lin, o_lvl = orc.lineage_from_parent(par)
+        assert torch.equal(lin, o_lin) and torch.equal(lvl, o_lvl)
+        assert fst.parent_from_lineage(lin, lvl).tolist() == par
+    with pytest.raises(ValueError):
+        fst.lineage_from_parent([-1, 2, 0])
+
+
+def test_workload_definitions():
+    from fstattention_b200 import configs
+    w = configs.workload("medusa256")
+    assert len(w.trees[0]) == 256 and w.heads == 32 and w.head_dim == 128 and w.block_m == 64
+    depth = [0] * 256
+    for i, p in enumerate(w.trees[0]):
+        depth[i] = 0 if p < 0 else depth[p] + 1
+    assert np.bincount(depth).tolist() == [1, 10, 36, 133, 76]
+    assert configs.workload("binary31").trees[0][:5] == [-1, 0, 0, 1, 1]
+    assert configs.workload("random1024", 3).trees[0] == configs.random_window_tree(3)
+    assert configs.workload("random1024", 3).trees[0] != configs.random_window_tree(4)
+    forest = configs.workload("forest64").trees
+    assert len(forest) == 64 and all(len(t) == 256 for t in forest)
+    deep = configs.workload("deep4096").trees[0]
+    assert len(deep) == 4096 and all(p < i for i, p in enumerate(deep))
+    assert len(configs.deep_chain_tree(0, 4096, chains=64)) == 2579

@@ -1,0 +1,170 @@
+"""GPU precompute kernel against the reference's own outputs (golden) and the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import unpack_golden_metadata
+from helpers import decode_packed
+from oracle import tree_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fst(built_lib):
+    import fstattention_b200
+    return fstattention_b200
+
+
+def test_metadata_bit_exact_vs_reference_golden(fst, metadata_golden):
+    for name, case in metadata_golden.items():
+        ai, am, li, bm, ma = unpack_golden_metadata(case)
+        meta = fst.build_tree_metadata(case["parent"].tolist(), bm, ma)
+        g_ai, g_am, g_li = meta
+        assert g_ai.dtype == torch.long and g_am.dtype == torch.bool and g_li.dtype == torch.long
+        assert torch.equal(g_ai.cpu(), ai), name
+        assert torch.equal(g_am.cpu(), am), name
+        assert torch.equal(g_li.cpu(), li), name
+        # the packed form says the same thing
+        nb = ai.shape[0]
+        cnt, p_idx, p_mask, p_leaf = decode_packed(meta.packed[0].cpu().numpy(), nb, bm, ma)
+        assert np.array_equal(cnt, (ai >= 0).sum(1).numpy()), name
+        assert np.array_equal(p_idx, ai.numpy()), name
+        assert np.array_equal(p_mask, am.numpy()), name
+        assert np.array_equal(p_leaf, li.numpy()), name
+
+
+def test_packed_only_matches(fst, metadata_golden):
+    case = metadata_golden["random1024_s1_bm64"]
+    ai, am, li, bm, ma = unpack_golden_metadata(case)
+    meta = fst.build_tree_metadata(case["parent"].tolist(), bm, ma, reference_format=False)
+    assert meta.ancestor_idx is None
+    cnt, p_idx, p_mask, p_leaf = decode_packed(meta.packed[0].cpu().numpy(), ai.shape[0], bm, ma)
+    assert np.array_equal(p_idx, ai.numpy()) and np.array_equal(p_mask, am.numpy())
+    assert np.array_equal(p_leaf, li.numpy())
+
+
+def test_batched_forest_vs_oracle(fst):
+    from fstattention_b200 import configs
+    forest = configs.jittered_forest(0, 64, 256)
+    meta = fst.build_tree_metadata(forest, 64, 64)
+    g_ai, g_am, g_li = (t.cpu() for t in meta)
+    assert g_ai.shape == (64, 4, 64) and g_am.shape == (64, 4, 64, 64) and g_li.shape == (64, 4, 64)
+    for t in range(0, 64, 7):
+        ai, am, li = orc.block_metadata_from_parent(forest[t], 64, 64)
+        assert torch.equal(g_ai[t], ai) and torch.equal(g_am[t], am) and torch.equal(g_li[t], li), t
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_trees_vs_oracle(fst, seed):
+    rng = np.random.RandomState(seed)
+    n = int(rng.randint(1, 700))
+    roots = int(rng.randint(1, 4))
+    window = int(rng.choice([2, 8, 64, 10_000]))
+    par = [-1] * min(roots, n) + [int(rng.randint(max(0, i - window), i)) for i in range(min(roots, n), n)]
+    bm = int(rng.choice([8, 16, 24, 64, 128]))
+    ai, am, li = orc.block_metadata_from_parent(par, bm, 4096)
+    ma = max(4, int((ai >= 0).sum(1).max()) + int(rng.randint(0, 9)))
+    ai, am, li = orc.block_metadata_from_parent(par, bm, ma)
+    g_ai, g_am, g_li = (t.cpu() for t in fst.build_tree_metadata(par, bm, ma))
+    assert torch.equal(g_ai, ai) and torch.equal(g_am, am) and torch.equal(g_li, li)
+
+
+def test_large_tree_attention_sets(fst):
+    """8192 nodes: every row's metadata set equals {itself} + its parent chain."""
+    from fstattention_b200 import configs
+    par = configs.random_window_tree(3, 8192, 64)
+    bm, ma = 64, 512
+    ai, am, li = (t.cpu().numpy() for t in fst.build_tree_metadata(par, bm, ma))
+    for b in range(ai.shape[0]):
+        row = ai[b][ai[b] >= 0]
+        assert np.all(np.diff(row) > 0)                      # ascending, unique
+    for k in range(0, 8192, 13):
+        b, j = divmod(k, bm)
+        got = set(ai[b][am[b, j]].tolist())
+        if li[b, j] >= 0:
+            assert li[b, j] == k
+            got.add(k)
+        want, x = {k}, par[k]
+        while x >= 0:
+            want.add(x)
+            x = par[x]
+        assert got == want, k
+
+
+def test_overflow_raises_and_gpu_stays_usable(fst, metadata_golden):
+    par = metadata_golden["medusa256_bm64"]["parent"].tolist()
+    with pytest.raises(RuntimeError, match="max_ancestors"):
+        fst.build_tree_metadata(par, 64, 16)
+    meta = fst.build_tree_metadata(par, 64, 16, check=False)     # no sync, no raise
+    assert int(meta.status[0].item()) == 17
+    # the first 16 ancestors of every block were kept
+    ai = orc.block_metadata_from_parent(par, 64, 64)[0]
+    assert torch.equal(meta.ancestor_idx.cpu(), ai[:, :16])
+    fst.build_tree_metadata(par, 64, 64)                         # still fine afterwards
+
+
+def test_malformed_parent_is_reported_not_faulted(fst):
+    par = [-1, 0, 1, 5, 2, 3]                                    # parent[3] = 5 points forward
+    with pytest.raises(ValueError, match="malformed"):
+        fst.build_tree_metadata(par, 16, 16)
+    with pytest.raises(ValueError, match="malformed"):
+        fst.build_tree_metadata([-1, 0, -7, 1], 16, 16)
+    fst.build_tree_metadata([-1, 0, 1, 2], 16, 16)
+
+
+def test_reference_signature_drop_in(fst, metadata_golden):
+    case = metadata_golden["reftree_d7_bm128"]
+    ai, am, li, bm, ma = unpack_golden_metadata(case)
+    lin, lvl = orc.lineage_from_parent(case["parent"].tolist())
+    lin_in = lin.clone()
+    g_ai, g_am, g_li = fst.create_fst_attention_kernel_inputs(lin_in, lvl, block_m=bm, max_ancestors=ma)
+    assert torch.equal(g_ai.cpu(), ai) and torch.equal(g_am.cpu(), am) and torch.equal(g_li.cpu(), li)
+    # side effect of the reference (utils.py:124-125): each node written into its own row
+    n = lin.shape[0]
+    want = lin.clone()
+    want[torch.arange(n), lvl] = torch.arange(n)
+    assert torch.equal(lin_in, want)
+    with pytest.raises(RuntimeError):
+        fst.create_fst_attention_kernel_inputs(lin.clone(), lvl, block_m=bm, max_ancestors=8)
+
+
+def test_out_buffers_are_reused(fst):
+    from fstattention_b200 import configs
+    meta = fst.build_tree_metadata(configs.random_window_tree(0), 64, 256)
+    ptr = meta.packed.data_ptr()
+    for s in (1, 2):
+        par = configs.random_window_tree(s)
+        fst.build_tree_metadata(par, 64, 256, out=meta)
+        ai, am, li = orc.block_metadata_from_parent(par, 64, 256)
+        assert meta.packed.data_ptr() == ptr
+        assert torch.equal(meta.ancestor_idx.cpu(), ai) and torch.equal(meta.ancestor_mask.cpu(), am)
+        assert torch.equal(meta.leaf_idx.cpu(), li)
+
+
+def test_pack_kernel_round_trip(fst, metadata_golden):
+    import ctypes
+    from fstattention_b200 import _lib
+    lib = _lib.lib()
+    for name in ("medusa256_bm64", "random1024_s0_bm64", "binary31_bm16", "multiroot157_bm32"):
+        case = metadata_golden[name]
+        ai, am, li, bm, ma = unpack_golden_metadata(case)
+        nb = ai.shape[0]
+        for base in (0, 128):
+            d_ai = (ai + base).cuda()            # sentinels shifted too, as the reference's test does
+            d_li = (li + base).cuda()
+            d_am = am.cuda()
+            nbytes = lib.fst_packed_meta_bytes(nb, bm, ma)
+            out = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+            status = torch.zeros(4, dtype=torch.int32, device="cuda")
+            rc = lib.fst_pack_metadata(d_ai.data_ptr(), d_am.data_ptr(), d_li.data_ptr(), 1, nb, bm, ma,
+                                       base, out.data_ptr(), nbytes, status.data_ptr(),
+                                       torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert status[0].item() == 0
+            ref = fst.build_tree_metadata(case["parent"].tolist(), bm, ma).packed[0]
+            got_parts = decode_packed(out.cpu().numpy(), nb, bm, ma)
+            ref_parts = decode_packed(ref.cpu().numpy(), nb, bm, ma)
+            for g, r in zip(got_parts, ref_parts):
+                assert np.array_equal(g, r), (name, base)
