@@ -9,11 +9,11 @@ cudaError_t launch_mma_f16_d128(const AttnArgs &, int, cudaStream_t);
 cudaError_t launch_mma_bf16_d64(const AttnArgs &, int, cudaStream_t);
 cudaError_t launch_mma_bf16_d128(const AttnArgs &, int, cudaStream_t);
 
-cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int tile_rows, cudaStream_t stream) {
-    if (dtype == FST_F16 && a.D == 64) return launch_mma_f16_d64(a, tile_rows, stream);
-    if (dtype == FST_F16 && a.D == 128) return launch_mma_f16_d128(a, tile_rows, stream);
-    if (dtype == FST_BF16 && a.D == 64) return launch_mma_bf16_d64(a, tile_rows, stream);
-    if (dtype == FST_BF16 && a.D == 128) return launch_mma_bf16_d128(a, tile_rows, stream);
+cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream) {
+    if (dtype == FST_F16 && a.D == 64) return launch_mma_f16_d64(a, variant, stream);
+    if (dtype == FST_F16 && a.D == 128) return launch_mma_f16_d128(a, variant, stream);
+    if (dtype == FST_BF16 && a.D == 64) return launch_mma_bf16_d64(a, variant, stream);
+    if (dtype == FST_BF16 && a.D == 128) return launch_mma_bf16_d128(a, variant, stream);
     return cudaErrorNotSupported;
 }
 
@@ -137,13 +137,13 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
 
     int choice = kernel;
     if (choice == FST_KERNEL_AUTO)
-        choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_MMA_T64
+        choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_MMA
                                                                     : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice != FST_KERNEL_MMA_T64 && choice != FST_KERNEL_MMA_T32) return FST_ERR_INVALID_ARG;
+    if (choice != FST_KERNEL_MMA) return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
-    return cuda_status(launch_attention_mma(a, dtype, choice == FST_KERNEL_MMA_T64 ? 64 : 32, st));
+    return cuda_status(launch_attention_mma(a, dtype, 0, st));
 }
 
 size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m, int max_ancestors) {

@@ -2,7 +2,7 @@
 #include "fst_attention_mma.cuh"
 
 namespace fst {
-cudaError_t launch_mma_f16_d64(const AttnArgs &a, int tile_rows, cudaStream_t stream) {
-    return launch_mma_d<__half, 64>(a, tile_rows, stream);
+cudaError_t launch_mma_f16_d64(const AttnArgs &a, int variant, cudaStream_t stream) {
+    return launch_mma_d<__half, 64>(a, variant, stream);
 }
 }  // namespace fst

@@ -1,8 +1,8 @@
 // Tree attention, fp32-arithmetic kernel for every dtype and head_dim in {16,32,64,128}.
 //
 // Computes what the reference's _fwd_kernel computes (fstattention.py:21-151): for each query
-// row of a block, softmax over {masked ancestors of the block's ancestor list} + {the row
-// itself when it is a block leaf} + {every shared-prefix row}, times V.  One warp owns one
+// row of a block, softmax over {its ancestors outside the block, from the block's gathered
+// list} + {itself and its ancestors inside the block} + {every shared-prefix row}, times V.  One warp owns one
 // query row at a time; keys are taken 32 at a time, one per lane, with an online softmax in
 // base 2 (scores are scaled by sm_scale*log2(e) like fstattention.py:59).  All arithmetic is
 // fp32, so fp32 inputs keep fp32 accuracy; this is the kernel for fp32 tensors, small head
@@ -39,8 +39,8 @@ attn_simt_kernel(const AttnArgs a) {
     const unsigned char *blob = a.packed + size_t(z) * a.meta_stride;
     const int count = min(max(reinterpret_cast<const int32_t *>(blob + L.off_count)[b], 0), a.ma);
     const int32_t *idx = reinterpret_cast<const int32_t *>(blob + L.off_idx) + size_t(b) * a.ma;
-    const uint32_t *mask = reinterpret_cast<const uint32_t *>(blob + L.off_mask) + size_t(b) * a.bm * L.maw;
-    const uint32_t *leaf = reinterpret_cast<const uint32_t *>(blob + L.off_leaf) + size_t(b) * L.lw;
+    const uint32_t *emask = reinterpret_cast<const uint32_t *>(blob + L.off_emask) + size_t(b) * a.bm * L.maw;
+    const uint32_t *bmask = reinterpret_cast<const uint32_t *>(blob + L.off_bmask) + size_t(b) * a.bm * L.bw;
 
     const T *qp = static_cast<const T *>(a.q) + z * a.qs_z + h * a.qs_h;
     const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
@@ -96,18 +96,21 @@ attn_simt_kernel(const AttnArgs a) {
             m = m_new;
         };
 
-        for (int a0 = 0; a0 < count; a0 += 32) {      // ancestors, gated by the row's mask bits
+        for (int a0 = 0; a0 < count; a0 += 32) {      // external ancestors, gated by mask bits
             const int s = a0 + lane;
             long long key = -1;
-            if (s < count && ((mask[j * L.maw + (s >> 5)] >> (s & 31)) & 1u)) {
+            if (s < count && ((emask[j * L.maw + (s >> 5)] >> (s & 31)) & 1u)) {
                 const int node = idx[s];
                 if (node >= 0 && node < a.n_q) key = a.prefix + node;
                 else report(a.status, FST_DEV_INDEX_RANGE, b, s);
             }
             absorb(key);
         }
-        if ((leaf[j >> 5] >> (j & 31)) & 1u)          // the row itself, through the leaf path
-            absorb(lane == 0 ? (long long)(a.prefix + row) : -1LL);
+        for (int c0 = 0; c0 < a.bm; c0 += 32) {       // the row itself and ancestors in the block
+            const int c = c0 + lane, node = b * a.bm + c;
+            const bool on = c < a.bm && ((bmask[j * L.bw + (c >> 5)] >> (c & 31)) & 1u) && node < a.n_q;
+            absorb(on ? (long long)(a.prefix + node) : -1LL);
+        }
         for (int p0 = 0; p0 < a.prefix; p0 += 32)     // shared prefix, dense
             absorb(p0 + lane < a.prefix ? (long long)(p0 + lane) : -1LL);
 

@@ -11,9 +11,14 @@
 namespace fst {
 
 // Offsets (bytes) of the four arrays inside one packed-metadata blob.
+//   count[nb]            external ancestors of the block (nodes outside the block's own rows)
+//   idx  [nb][ma]        their node indices, ascending, -1 padded
+//   emask[nb][bm][maw]   bit a of row j: row j attends to external ancestor slot a
+//   bmask[nb][bm][bw]    bit c of row j: row j attends to row c of its own block (c == j always
+//                        set; other bits are ancestors that live inside the block)
 struct PackedLayout {
-    int nb, bm, ma, maw, lw;
-    size_t off_count, off_idx, off_mask, off_leaf, total;
+    int nb, bm, ma, maw, bw;
+    size_t off_count, off_idx, off_emask, off_bmask, total;
 };
 
 __host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~size_t(15); }
@@ -22,12 +27,12 @@ __host__ __device__ inline PackedLayout packed_layout(int nb, int bm, int ma) {
     PackedLayout L;
     L.nb = nb; L.bm = bm; L.ma = ma;
     L.maw = (ma + 31) / 32;
-    L.lw = (bm + 31) / 32;
+    L.bw = (bm + 31) / 32;
     L.off_count = 0;
     L.off_idx = align16(size_t(nb) * 4);
-    L.off_mask = L.off_idx + align16(size_t(nb) * ma * 4);
-    L.off_leaf = L.off_mask + align16(size_t(nb) * bm * L.maw * 4);
-    L.total = L.off_leaf + align16(size_t(nb) * L.lw * 4);
+    L.off_emask = L.off_idx + align16(size_t(nb) * ma * 4);
+    L.off_bmask = L.off_emask + align16(size_t(nb) * bm * L.maw * 4);
+    L.total = L.off_bmask + align16(size_t(nb) * bm * L.bw * 4);
     return L;
 }
 
@@ -65,6 +70,6 @@ struct AttnArgs {
 
 cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);
 // returns cudaErrorNotSupported when no tensor-core instantiation fits
-cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int tile_rows, cudaStream_t stream);
+cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream);
 
 }  // namespace fst

@@ -9,9 +9,17 @@
 // CTA per (tree, block) marks ancestors in a shared-memory bitmap by walking parent links,
 // ranks the set bits with a popcount prefix scan (which yields the ascending order of
 // torch.unique without sorting) and walks each row's chain once more to set its mask bits.
-// Integer work only; the outputs are bit-identical to the reference's.
+// Integer work only; the reference-format outputs are bit-identical to the reference's.
+//
+// The packed form written for the attention kernels splits A_b in two: ancestors outside the
+// block's own rows ("external", gathered row by row) and ancestors inside it, which the kernel
+// reads from the block's contiguous K/V rows through a row-by-row bit mask that also carries
+// the self bit (the reference's leaf path, utils.py:121-122, and its self-through-mask case,
+// utils.py:124-127, become the diagonal of that mask).
 //
 // Also here: the converter from reference-format metadata tensors to the packed form.
+
+#include <climits>
 
 #include "fst_common.cuh"
 
@@ -36,8 +44,10 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
 
     uint32_t *bitmap = reinterpret_cast<uint32_t *>(smem_raw);
     int *rank = reinterpret_cast<int *>(bitmap + W);     // set bits in words below w
-    uint32_t *rowmask = reinterpret_cast<uint32_t *>(rank + W);
-    int *warp_tot = reinterpret_cast<int *>(rowmask + size_t(bm) * maw);
+    const int bw = (bm + 31) >> 5;
+    uint32_t *rowmask = reinterpret_cast<uint32_t *>(rank + W);      // [bm][maw] over all of A_b
+    uint32_t *blkmask = rowmask + size_t(bm) * maw;                   // [bm][bw] over block rows
+    int *warp_tot = reinterpret_cast<int *>(blkmask + size_t(bm) * bw);
     int *s_par = warp_tot + 40;
 
     const int32_t *parent = parent_all + size_t(tree) * n_nodes;
@@ -45,6 +55,7 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     for (int i = tid; i < cap; i += PRE_THREADS) s_par[i] = parent[i];
     for (int i = tid; i < W; i += PRE_THREADS) bitmap[i] = 0u;
     for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
+    for (int i = tid; i < bm * bw; i += PRE_THREADS) blkmask[i] = 0u;
     __syncthreads();
 
     // parent of x; a malformed entry is reported and treated as a root, so every walk ends
@@ -57,17 +68,21 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
         return p;
     };
 
-    // 1. mark every strict ancestor of the block's rows.  A walker that finds a bit already set
-    //    stops: whoever set it keeps climbing, so everything above is (or will be) marked.
+    // 1. mark every strict ancestor of the block's rows.  A walker that sees a bit already set
+    //    stops: whoever set it keeps climbing, so everything above is (or will be) marked.  The
+    //    test is a plain read (a stale 0 only costs a redundant climb) and the set is a
+    //    fire-and-forget atomic, so a step costs one shared-memory round trip.
     for (int j = tid; j < bm; j += PRE_THREADS) {
         const int k = row0 + j;
         if (k < n_nodes) {
             int a = par(k);
             while (a >= 0) {
                 const uint32_t bit = 1u << (a & 31);
-                const uint32_t old = atomicOr(&bitmap[a >> 5], bit);
-                if (old & bit) break;
-                a = par(a);
+                const uint32_t seen = *reinterpret_cast<volatile uint32_t *>(&bitmap[a >> 5]);
+                const int up = par(a);
+                if (seen & bit) break;
+                atomicOr(&bitmap[a >> 5], bit);
+                a = up;
             }
         }
     }
@@ -109,15 +124,17 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     const int n_keep = min(n_anc, ma);
     if (n_anc > ma && tid == 0) report(status, FST_DEV_ANCESTOR_OVERFLOW, tree * 65536 + b, n_anc);
     __syncthreads();
+    // external ancestors are the ones below row0; they come first in ascending order
+    const int n_ext = min(ma, rank[row0 >> 5] + __popc(bitmap[row0 >> 5] & ((1u << (row0 & 31)) - 1u)));
 
     const PackedLayout L = packed_layout(nb, bm, ma);
     unsigned char *blob = packed_all ? packed_all + size_t(tree) * packed_stride : nullptr;
     int32_t *p_count = blob ? reinterpret_cast<int32_t *>(blob + L.off_count) : nullptr;
     int32_t *p_idx = blob ? reinterpret_cast<int32_t *>(blob + L.off_idx) + size_t(b) * ma : nullptr;
-    uint32_t *p_mask = blob ? reinterpret_cast<uint32_t *>(blob + L.off_mask) + size_t(b) * bm * maw
-                            : nullptr;
-    uint32_t *p_leaf = blob ? reinterpret_cast<uint32_t *>(blob + L.off_leaf) + size_t(b) * L.lw
-                            : nullptr;
+    uint32_t *p_emask = blob ? reinterpret_cast<uint32_t *>(blob + L.off_emask) + size_t(b) * bm * maw
+                             : nullptr;
+    uint32_t *p_bmask = blob ? reinterpret_cast<uint32_t *>(blob + L.off_bmask) + size_t(b) * bm * bw
+                             : nullptr;
     const size_t blk = size_t(tree) * nb + b;
     int64_t *o_idx = anc_idx_all ? anc_idx_all + blk * ma : nullptr;
     uint8_t *o_mask = anc_mask_all ? anc_mask_all + blk * size_t(bm) * ma : nullptr;
@@ -132,38 +149,47 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
             bits &= bits - 1;
             if (pos < ma) {
                 const int node = w * 32 + bit;
-                if (p_idx) p_idx[pos] = node;
+                if (p_idx && node < row0) p_idx[pos] = node;
                 if (o_idx) o_idx[pos] = node;
             }
             ++pos;
         }
     }
-    for (int a = n_keep + tid; a < ma; a += PRE_THREADS) {
-        if (p_idx) p_idx[a] = -1;
-        if (o_idx) o_idx[a] = -1;
-    }
-    if (tid == 0 && p_count) p_count[b] = n_keep;
+    if (p_idx)
+        for (int a = n_ext + tid; a < ma; a += PRE_THREADS) p_idx[a] = -1;
+    if (o_idx)
+        for (int a = n_keep + tid; a < ma; a += PRE_THREADS) o_idx[a] = -1;
+    if (tid == 0 && p_count) p_count[b] = n_ext;
 
     // 4. mask rows: the node itself (when it is somebody's ancestor in this block) and its chain
     for (int j = tid; j < bm; j += PRE_THREADS) {
         const int k = row0 + j;
+        blkmask[j * bw + (j >> 5)] |= 1u << (j & 31);     // every row attends to itself
         if (k < n_nodes) {
             int x = k;
             while (x >= 0) {
                 const uint32_t word = bitmap[x >> 5];
                 const uint32_t bit = 1u << (x & 31);
+                const int up = par(x);
                 if (word & bit) {
                     const int pos = rank[x >> 5] + __popc(word & (bit - 1u));
                     if (pos < ma) rowmask[j * maw + (pos >> 5)] |= 1u << (pos & 31);
+                    if (x >= row0) blkmask[j * bw + ((x - row0) >> 5)] |= 1u << ((x - row0) & 31);
                 }
-                x = par(x);
+                x = up;
             }
         }
     }
     __syncthreads();
 
-    if (p_mask)
-        for (int i = tid; i < bm * maw; i += PRE_THREADS) p_mask[i] = rowmask[i];
+    if (p_emask) {
+        for (int i = tid; i < bm * maw; i += PRE_THREADS) {
+            const int w = i % maw, lo = w * 32;           // keep the bits of external slots only
+            const uint32_t keep = n_ext >= lo + 32 ? 0xffffffffu : (n_ext > lo ? (1u << (n_ext - lo)) - 1u : 0u);
+            p_emask[i] = rowmask[i] & keep;
+        }
+        for (int i = tid; i < bm * bw; i += PRE_THREADS) p_bmask[i] = blkmask[i];
+    }
     if (o_mask) {
         if ((ma & 3) == 0) {                             // four bool bytes per store
             uint32_t *o32 = reinterpret_cast<uint32_t *>(o_mask);
@@ -182,13 +208,12 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     }
 
     // 5. leaves: block rows that are not in the ancestor set (rows past the last node too)
-    for (int j0 = 0; j0 < bm; j0 += PRE_THREADS) {
-        const int j = j0 + tid, k = row0 + j;
-        const bool leaf = j < bm && !((bitmap[k >> 5] >> (k & 31)) & 1u);
-        if (j < bm && o_leaf) o_leaf[j] = leaf ? int64_t(k) : int64_t(-1);
-        const uint32_t word = __ballot_sync(0xffffffffu, leaf);
-        if (lane == 0 && (j0 + wid * 32) < bm && p_leaf) p_leaf[(j0 >> 5) + wid] = word;
-    }
+    if (o_leaf)
+        for (int j = tid; j < bm; j += PRE_THREADS) {
+            const int k = row0 + j;
+            const bool leaf = !((bitmap[k >> 5] >> (k & 31)) & 1u);
+            o_leaf[j] = leaf ? int64_t(k) : int64_t(-1);
+        }
 }
 
 // -------------------------------------------------------------------------------------------
@@ -203,63 +228,86 @@ pack_kernel(const int64_t *__restrict__ anc_idx_all, const uint8_t *__restrict__
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int b = blockIdx.x, tree = blockIdx.y, nb = gridDim.x;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int maw = (ma + 31) >> 5;
-    uint32_t *valid = reinterpret_cast<uint32_t *>(smem_raw);      // [maw]
-    __shared__ int s_count;
-    if (tid == 0) s_count = 0;
-    for (int i = tid; i < maw; i += PACK_THREADS) valid[i] = 0u;
+    const int maw = (ma + 31) >> 5, bw = (bm + 31) >> 5;
+    // slot -> external position (>= 0), or -1 - column for an ancestor inside the block, or
+    // INT_MIN for padding
+    int *slot_map = reinterpret_cast<int *>(smem_raw);               // [ma]
+    __shared__ int s_warp[PACK_THREADS / 32];
+    __shared__ int s_base;
+    if (tid == 0) s_base = 0;
     __syncthreads();
 
     const PackedLayout L = packed_layout(nb, bm, ma);
     unsigned char *blob = packed_all + size_t(tree) * packed_stride;
     int32_t *p_count = reinterpret_cast<int32_t *>(blob + L.off_count);
     int32_t *p_idx = reinterpret_cast<int32_t *>(blob + L.off_idx) + size_t(b) * ma;
-    uint32_t *p_mask = reinterpret_cast<uint32_t *>(blob + L.off_mask) + size_t(b) * bm * maw;
-    uint32_t *p_leaf = reinterpret_cast<uint32_t *>(blob + L.off_leaf) + size_t(b) * L.lw;
+    uint32_t *p_emask = reinterpret_cast<uint32_t *>(blob + L.off_emask) + size_t(b) * bm * maw;
+    uint32_t *p_bmask = reinterpret_cast<uint32_t *>(blob + L.off_bmask) + size_t(b) * bm * bw;
     const size_t blk = size_t(tree) * nb + b;
     const int64_t *g_idx = anc_idx_all + blk * ma;
     const uint8_t *g_mask = anc_mask_all + blk * size_t(bm) * ma;
     const int64_t *g_leaf = leaf_idx_all + blk * bm;
+    const int64_t row0 = int64_t(b) * bm;
 
-    for (int a = tid; a < ma; a += PACK_THREADS) {
-        const int64_t v = g_idx[a];
-        const int64_t rel = v - index_base;
-        const bool ok = v >= 0 && rel >= 0;
-        int32_t out = -1;
-        if (ok) {
-            if (rel > 0x7fffffffLL) {
-                report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, a);
-            } else {
-                out = int32_t(rel);
-                atomicOr(&valid[a >> 5], 1u << (a & 31));
-                atomicMax(&s_count, a + 1);
+    // external slots keep their order; an exclusive scan of the "is external" flags places them
+    for (int a0 = 0; a0 < ma; a0 += PACK_THREADS) {
+        const int a = a0 + tid;
+        bool ext = false;
+        int node = -1;
+        int code = INT_MIN;
+        if (a < ma) {
+            const int64_t v = g_idx[a];
+            const int64_t rel = v - index_base;
+            if (v >= 0 && rel >= 0) {
+                if (rel > 0x7fffffffLL) {
+                    report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, a);
+                } else if (rel >= row0 && rel < row0 + bm) {
+                    code = -1 - int(rel - row0);
+                } else {
+                    ext = true;
+                    node = int(rel);
+                }
             }
         }
-        p_idx[a] = out;
-    }
-    __syncthreads();
-    if (tid == 0) p_count[b] = s_count;
-
-    for (int i = tid; i < bm * maw; i += PACK_THREADS) {
-        const int j = i / maw, w = i - j * maw;
-        const uint8_t *src = g_mask + size_t(j) * ma + w * 32;
-        const int n = min(32, ma - w * 32);
-        uint32_t word = 0u;
-        for (int a = 0; a < n; ++a) word |= (src[a] ? 1u : 0u) << a;
-        p_mask[i] = word & valid[w];
-    }
-
-    for (int j0 = 0; j0 < bm; j0 += PACK_THREADS) {
-        const int j = j0 + tid;
-        bool leaf = false;
-        if (j < bm) {
-            const int64_t v = g_leaf[j];
-            leaf = v >= 0 && v >= index_base;
-            if (leaf && v - index_base != int64_t(b) * bm + j)
-                report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, -1 - j);
+        const uint32_t votes = __ballot_sync(0xffffffffu, ext);
+        if (lane == 0) s_warp[wid] = __popc(votes);
+        __syncthreads();
+        int pos = s_base + __popc(votes & ((1u << lane) - 1u));
+        for (int w = 0; w < wid; ++w) pos += s_warp[w];
+        if (ext) {
+            code = pos;
+            p_idx[pos] = node;
         }
-        const uint32_t word = __ballot_sync(0xffffffffu, leaf);
-        if (lane == 0 && (j0 + wid * 32) < bm) p_leaf[(j0 >> 5) + wid] = word;
+        if (a < ma) slot_map[a] = code;
+        __syncthreads();
+        if (tid == 0) {
+            int add = 0;
+            for (int w = 0; w < PACK_THREADS / 32; ++w) add += s_warp[w];
+            s_base += add;
+        }
+        __syncthreads();
+    }
+    const int n_ext = s_base;
+    for (int a = n_ext + tid; a < ma; a += PACK_THREADS) p_idx[a] = -1;
+    if (tid == 0) p_count[b] = n_ext;
+
+    // one thread per row: scatter its mask bytes into the two bit masks
+    for (int j = tid; j < bm; j += PACK_THREADS) {
+        uint32_t *er = p_emask + size_t(j) * maw, *br = p_bmask + size_t(j) * bw;
+        for (int w = 0; w < maw; ++w) er[w] = 0u;
+        for (int w = 0; w < bw; ++w) br[w] = 0u;
+        const int64_t leaf = g_leaf[j];
+        const bool is_leaf = leaf >= 0 && leaf >= index_base;
+        if (is_leaf && leaf - index_base != row0 + j)
+            report(status, FST_DEV_INDEX_RANGE, tree * 65536 + b, -1 - j);
+        if (is_leaf) br[j >> 5] |= 1u << (j & 31);
+        const uint8_t *src = g_mask + size_t(j) * ma;
+        for (int a = 0; a < ma; ++a) {
+            if (!src[a]) continue;
+            const int code = slot_map[a];
+            if (code >= 0) er[code >> 5] |= 1u << (code & 31);
+            else if (code != INT_MIN) br[(-1 - code) >> 5] |= 1u << ((-1 - code) & 31);
+        }
     }
 }
 
@@ -272,7 +320,7 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
     const int nb = (n_nodes + bm - 1) / bm;
     const int maw = (ma + 31) / 32;
     const size_t W = (size_t(nb) * bm + 31) / 32;
-    const size_t fixed = (2 * W + size_t(bm) * maw + 40) * 4;
+    const size_t fixed = (2 * W + size_t(bm) * maw + size_t(bm) * ((bm + 31) / 32) + 40) * 4;
     const size_t budget = 200 * 1024;
     if (fixed + 1024 > budget) return cudaErrorInvalidValue;
     const size_t cap = (budget - fixed) / 4;
@@ -294,9 +342,8 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
 cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
                         int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
                         size_t packed_stride, int32_t *status, cudaStream_t stream) {
-    const int maw = (ma + 31) / 32;
     dim3 grid(nb, n_trees);
-    pack_kernel<<<grid, PACK_THREADS, size_t(maw) * 4, stream>>>(
+    pack_kernel<<<grid, PACK_THREADS, size_t(ma) * 4, stream>>>(
         anc_idx, anc_mask, leaf_idx, bm, ma, index_base, static_cast<unsigned char *>(packed),
         packed_stride, status);
     return cudaGetLastError();

@@ -46,8 +46,7 @@ enum fst_dtype { FST_F16 = 0, FST_BF16 = 1, FST_F32 = 2 };
 enum fst_kernel {
     FST_KERNEL_AUTO = 0,
     FST_KERNEL_SIMT = 1,           /* fp32 arithmetic, any dtype / head_dim in {16,32,64,128}   */
-    FST_KERNEL_MMA_T64 = 2,        /* tensor-core kernel, 64-row K/V tiles                      */
-    FST_KERNEL_MMA_T32 = 3         /* tensor-core kernel, 32-row K/V tiles (more CTAs per SM)   */
+    FST_KERNEL_MMA = 2             /* tensor-core kernel: fp16/bf16, head_dim 64/128            */
 };
 
 int fst_version(void);
@@ -57,12 +56,16 @@ const char *fst_status_string(int status);
  * Packed block metadata, the form the attention kernels read.  For one tree with
  * n_blocks = ceil(n_nodes / block_m) query blocks it is one blob of
  * fst_packed_meta_bytes() bytes holding four arrays, each starting on a 16-byte boundary:
- *   int32  count[n_blocks]                 unique ancestors of the block
- *   int32  idx  [n_blocks][max_ancestors]  their node indices, ascending, -1 padded
- *   uint32 mask [n_blocks][block_m][W]     W = ceil(max_ancestors/32); bit a of row j set when
- *                                          row j attends to ancestor slot a
- *   uint32 leaf [n_blocks][ceil(block_m/32)] bit j set when row j attends to itself through
- *                                          the leaf path (it is not in the block's ancestor list)
+ *   int32  count[n_blocks]                 ancestors of the block that lie outside its own rows
+ *   int32  idx  [n_blocks][max_ancestors]  their node indices, in list order, -1 padded
+ *   uint32 emask[n_blocks][block_m][W]     W = ceil(max_ancestors/32); bit a of row j set when
+ *                                          row j attends to idx[a]
+ *   uint32 bmask[n_blocks][block_m][ceil(block_m/32)]
+ *                                          bit c of row j set when row j attends to row c of
+ *                                          its own block: itself (always) and the ancestors
+ *                                          that live inside the block
+ * The reference's ancestor list is the external list followed by the in-block ancestors; its
+ * leaf path (utils.py:121-122) is the diagonal of bmask.
  * Indices are relative to the first tree row (the shared prefix is not counted).
  * A batch of trees is an array of such blobs, meta_tree_stride bytes apart.
  */

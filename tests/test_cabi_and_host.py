@@ -28,8 +28,8 @@ def test_host_only_entry_points(built_lib):
     assert lib.fst_version() == 100
     assert "max_ancestors" in _lib.status_string(17)
     assert _lib.status_string(0) == "ok"
-    # layout: count | idx | mask | leaf, every part 16-byte aligned
-    assert lib.fst_packed_meta_bytes(4, 64, 64) == 16 + 4 * 64 * 4 + 4 * 64 * 2 * 4 + 32
+    # layout: count | idx | emask | bmask, every part 16-byte aligned
+    assert lib.fst_packed_meta_bytes(4, 64, 64) == 16 + 4 * 64 * 4 + 4 * 64 * 2 * 4 + 4 * 64 * 2 * 4
     assert lib.fst_packed_meta_bytes(0, 64, 64) == 0
     assert lib.fst_attention_ref_workspace_bytes(2, 256, 64, 64) == 2 * lib.fst_packed_meta_bytes(4, 64, 64)
     # argument checks happen before any CUDA call

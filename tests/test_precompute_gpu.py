@@ -28,7 +28,9 @@ def test_metadata_bit_exact_vs_reference_golden(fst, metadata_golden):
         # the packed form says the same thing
         nb = ai.shape[0]
         cnt, p_idx, p_mask, p_leaf = decode_packed(meta.packed[0].cpu().numpy(), nb, bm, ma)
-        assert np.array_equal(cnt, (ai >= 0).sum(1).numpy()), name
+        lo = torch.arange(nb)[:, None] * bm
+        external = (ai >= 0) & ((ai < lo) | (ai >= lo + bm))
+        assert np.array_equal(cnt, external.sum(1).numpy()), name
         assert np.array_equal(p_idx, ai.numpy()), name
         assert np.array_equal(p_mask, am.numpy()), name
         assert np.array_equal(p_leaf, li.numpy()), name
