@@ -33,6 +33,28 @@ static int cuda_status(cudaError_t e) {
 
 using namespace fst;
 
+// Scratch for fst_attention_fwd_ref_static: lives in the library's device image, so every GPU
+// that loads the library carries these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[FST_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not something a kernel can dereference, so the address is
+// asked for once per device and remembered.
+static int static_scratch_address(void **out) {
+    constexpr int kMaxDevices = 64;
+    static void *cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FST_ERR_CUDA;
+    if (cached[dev] == nullptr) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr)
+            return FST_ERR_CUDA;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return FST_OK;
+}
+
 extern "C" {
 
 int fst_version(void) { return FST_VERSION; }
@@ -45,7 +67,7 @@ const char *fst_status_string(int s) {
         case FST_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
         case FST_ERR_WORKSPACE: return "workspace too small";
         case FST_ERR_CUDA: return "CUDA runtime error";
-        case FST_ERR_TOO_LARGE: return "size beyond the supported limit";
+        case FST_ERR_TOO_LARGE: return "size beyond the supported limit (or beyond the built-in scratch)";
         case FST_DEV_MALFORMED_TREE: return "malformed tree: parent[i] must be -1 or an earlier node";
         case FST_DEV_ANCESTOR_OVERFLOW: return "a block has more unique ancestors than max_ancestors";
         case FST_DEV_INDEX_RANGE: return "metadata index outside the K/V rows";
@@ -177,6 +199,29 @@ int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, 
                              k_stride_h, k_stride_n, v_stride_z, v_stride_h, v_stride_n, o_stride_z,
                              o_stride_h, o_stride_n, block_m, max_ancestors, sm_scale, dtype, kernel,
                              status, stream);
+}
+
+int fst_attention_fwd_ref_static(const void *q, const void *k, const void *v, void *o, float *lse,
+                                 const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                                 const int64_t *leaf_idx, int n_meta_trees, int Z, int H, int n_q,
+                                 int n_kv, int head_dim, int64_t q_stride_z, int64_t q_stride_h,
+                                 int64_t q_stride_n, int64_t k_stride_z, int64_t k_stride_h,
+                                 int64_t k_stride_n, int64_t v_stride_z, int64_t v_stride_h,
+                                 int64_t v_stride_n, int64_t o_stride_z, int64_t o_stride_h,
+                                 int64_t o_stride_n, int block_m, int max_ancestors, float sm_scale,
+                                 int dtype, int kernel, int32_t *status, void *stream) {
+    if (n_meta_trees <= 0 || n_q <= 0 || block_m <= 0 || max_ancestors <= 0) return FST_ERR_INVALID_ARG;
+    const size_t need = fst_attention_ref_workspace_bytes(n_meta_trees, n_q, block_m, max_ancestors);
+    if (need == 0) return FST_ERR_INVALID_ARG;
+    if (need > FST_STATIC_SCRATCH_BYTES) return FST_ERR_TOO_LARGE;   // metadata does not fit the built-in scratch
+    void *scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != FST_OK) return rc;
+    return fst_attention_fwd_ref(q, k, v, o, lse, ancestor_idx, ancestor_mask, leaf_idx, n_meta_trees,
+                                 Z, H, n_q, n_kv, head_dim, q_stride_z, q_stride_h, q_stride_n,
+                                 k_stride_z, k_stride_h, k_stride_n, v_stride_z, v_stride_h, v_stride_n,
+                                 o_stride_z, o_stride_h, o_stride_n, block_m, max_ancestors, sm_scale,
+                                 dtype, kernel, scratch, FST_STATIC_SCRATCH_BYTES, status, stream);
 }
 
 }  // extern "C"

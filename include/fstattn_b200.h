@@ -154,6 +154,40 @@ int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, 
                           void *workspace, size_t workspace_bytes,
                           int32_t *status, void *stream);
 
+/*
+ * fst_attention_fwd_ref for hosts that must not allocate.  (No counterpart in the reference,
+ * whose wrapper allocates freely through torch, fstattention.py:158-160.)
+ *
+ * Some callers cannot provide the workspace above because they cannot call cudaMalloc or a
+ * framework allocator where this function runs: an inference engine's per-layer plugin hook
+ * that is only handed its input and output buffers, or a serving loop that gave all device
+ * memory to its own pool at start-up and forbids (or cannot afford, since cudaMalloc
+ * synchronises the device) allocation on the decode path.  For them the packed metadata is
+ * written into a fixed array of FST_STATIC_SCRATCH_BYTES bytes that is part of the library's
+ * device image; inputs and outputs are still the caller's.
+ *
+ *   - Metadata whose packed form (fst_attention_ref_workspace_bytes) exceeds
+ *     FST_STATIC_SCRATCH_BYTES is refused with FST_ERR_TOO_LARGE and nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call before any stream
+ *     capture begins.  Later calls only launch kernels.  No call allocates or frees memory.
+ *   - All calls on a device share the one array and it keeps whatever the last call wrote;
+ *     every call rewrites all of it that it reads, so nothing has to be cleared.  Two calls
+ *     whose kernels can overlap on the GPU (different streams without ordering) race on it:
+ *     keep calls on one stream or order them with events.
+ */
+#define FST_STATIC_SCRATCH_BYTES (512 * 1024)
+int fst_attention_fwd_ref_static(const void *q, const void *k, const void *v, void *o, float *lse,
+                                 const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
+                                 const int64_t *leaf_idx, int n_meta_trees,
+                                 int Z, int H, int n_q, int n_kv, int head_dim,
+                                 int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                                 int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                                 int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                                 int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                                 int block_m, int max_ancestors, float sm_scale, int dtype,
+                                 int kernel, int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
