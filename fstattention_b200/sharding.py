@@ -1,0 +1,81 @@
+"""Multi-GPU partitioning of tree attention: by independent trees or by heads.
+
+Every (tree, head, query block) is independent (the reference's programs never communicate,
+fstattention.py:42-45), so the path shards without any exchange inside it: a batch of trees is
+split over the ranks tree-wise, a single large tree head-wise.  The only collective is the
+all-gather that reassembles the output, and callers that keep the output sharded for the next
+layer skip even that (``gather=False``).  One process per GPU; ``torch.distributed`` (NCCL on
+GPUs) does the gather.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+AXES = {"tree": 0, "head": 1}
+
+
+def shard_bounds(n_units: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous balanced split: the first ``n_units % world`` ranks hold one unit more."""
+    if not (0 <= rank < world):
+        raise ValueError("rank outside the world")
+    base, extra = divmod(n_units, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def local_slice(t: torch.Tensor, axis: str, world: int, rank: int) -> torch.Tensor:
+    """This rank's part of a full ``[Z, H, N, D]`` tensor (a view)."""
+    dim = AXES[axis]
+    lo, hi = shard_bounds(t.shape[dim], world, rank)
+    return t.narrow(dim, lo, hi - lo)
+
+
+def all_gather_outputs(o_local: torch.Tensor, axis: str, n_total: int, group=None) -> torch.Tensor:
+    """Reassemble the full output from every rank's shard along ``axis``.
+
+    Equal shards that are contiguous in the full tensor (tree axis, or head axis with Z == 1)
+    are gathered in place into one buffer; otherwise shards are padded to the largest one,
+    gathered and trimmed.
+    """
+    world = dist.get_world_size(group)
+    dim = AXES[axis]
+    sizes = [hi - lo for lo, hi in (shard_bounds(n_total, world, r) for r in range(world))]
+    if o_local.shape[dim] != sizes[dist.get_rank(group)]:
+        raise ValueError("local shard does not match the partition")
+    full_shape = list(o_local.shape)
+    full_shape[dim] = n_total
+    in_place = len(set(sizes)) == 1 and (dim == 0 or o_local.shape[0] == 1)
+    if in_place:
+        full = torch.empty(full_shape, dtype=o_local.dtype, device=o_local.device)
+        dist.all_gather_into_tensor(full.view(-1), o_local.contiguous().view(-1), group=group)
+        return full
+    pad_shape = list(o_local.shape)
+    pad_shape[dim] = max(sizes)
+    padded = torch.zeros(pad_shape, dtype=o_local.dtype, device=o_local.device)
+    padded.narrow(dim, 0, o_local.shape[dim]).copy_(o_local)
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
+
+
+def sharded_fst_attention(q_local, k_local, v_local, meta_local, sm_scale: float, axis: str,
+                          n_total: int, *, group=None, gather: bool = True,
+                          attention: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+    """Tree attention on this rank's shard, then (optionally) the all-gather of outputs.
+
+    ``axis="tree"``: the tensors hold this rank's trees (batch elements) and ``meta_local``
+    their metadata.  ``axis="head"``: the tensors hold this rank's heads of every batch element
+    and ``meta_local`` is the full tree metadata, identical on all ranks.  ``n_total`` is the
+    global number of trees or heads.
+    """
+    if axis not in AXES:
+        raise ValueError("axis must be 'tree' or 'head'")
+    if attention is None:
+        from .fstattention import fst_attention as attention
+    o_local = attention(q_local, k_local, v_local, meta_local, sm_scale=sm_scale, **kwargs)
+    if not gather or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return o_local
+    return all_gather_outputs(o_local, axis, n_total, group)
