@@ -90,6 +90,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int MMA_TN = 32;                                // K/V rows per column tile
 
+__device__ __forceinline__ int nt_ext_of(int count, int ma) {   // external-ancestor tiles
+    return (min(max(count, 0), ma) + MMA_TN - 1) / MMA_TN;
+}
+
 template <int D, int BM>
 struct MmaSmem {
     static constexpr int RS = D * 2 + 16;                 // padded row, bytes
@@ -138,6 +142,39 @@ attn_mma_kernel(const AttnArgs a) {
     T *op = static_cast<T *>(a.o) + z * a.os_z + h * a.os_h;
 
     const int lr = tid / CH, lc = tid % CH;               // my row-in-pass and 16-byte chunk
+    constexpr int SPT = TN / RPP;                         // gathered rows per thread and tile
+    static_assert(TN % RPP == 0, "a gathered tile must be whole passes");
+
+    // A warp issues in order, so a load result must not be touched before everything that does
+    // not depend on it has been requested.  Order: index list and count (plain loads), Q
+    // fragments, the block's own rows (cp.async), and only then the gathered rows, whose
+    // addresses need the indices.
+    const int r0 = warp * 16 + g, r1 = r0 + 8;            // my two rows inside the block
+    const bool ok0 = row0 + r0 < n_q, ok1 = row0 + r1 < n_q;
+
+    int nodeA[SPT], nodeB[SPT];                           // my slots of the next two external tiles
+    auto fetch_idx = [&](int e, int (&node)[SPT]) {       // the index list is -1 padded
+#pragma unroll
+        for (int j = 0; j < SPT; ++j) {
+            const int slot = e * TN + lr + j * RPP;
+            node[j] = slot < a.ma ? __ldg(g_idx + slot) : -1;
+        }
+    };
+    fetch_idx(0, nodeA);
+    fetch_idx(1, nodeB);
+
+    uint32_t qf[KS][4];
+    {
+        const uint32_t *q0 = reinterpret_cast<const uint32_t *>(qp + (long long)(ok0 ? row0 + r0 : 0) * a.qs_n) + t;
+        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(qp + (long long)(ok1 ? row0 + r1 : 0) * a.qs_n) + t;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qf[ks][0] = ok0 ? __ldg(q0 + ks * 8) : 0u;
+            qf[ks][1] = ok1 ? __ldg(q1 + ks * 8) : 0u;
+            qf[ks][2] = ok0 ? __ldg(q0 + ks * 8 + 4) : 0u;
+            qf[ks][3] = ok1 ? __ldg(q1 + ks * 8 + 4) : 0u;
+        }
+    }
 
     // ---- the block's own K and V rows: contiguous, no metadata needed
     auto load_block = [&](const T *base, int64_t stride_n, int smem_off) {
@@ -154,24 +191,20 @@ attn_mma_kernel(const AttnArgs a) {
     cp_async_commit();                                    // group 1
 
     // ---- gathered tiles: external ancestors first, then the prefix
-    count = min(max(count, 0), a.ma);
-    const int nt_ext = (count + TN - 1) / TN;
-    const int nt_gat = nt_ext + (prefix + TN - 1) / TN;
-    auto load_gathered = [&](int e, int st, bool ext) {   // K and V rows of gathered tile e
+    auto load_gathered = [&](int e, int st, bool ext, const int (&node)[SPT]) {
         const uint32_t kd = s_base + SM::KE + st * TN * RS + lc * 16;
         const uint32_t vd = s_base + SM::VE + st * TN * RS + lc * 16;
 #pragma unroll
-        for (int s = lr; s < TN; s += RPP) {
+        for (int j = 0; j < SPT; ++j) {
+            const int s = lr + j * RPP;
             long long rr = 0;
             bool ok;
-            if (ext) {                                    // the index list is -1 padded
-                const int slot = e * TN + s;
-                const int node = slot < a.ma ? __ldg(g_idx + slot) : -1;
-                ok = node >= 0 && node < n_q;
-                if (node >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, slot);
-                if (ok) rr = prefix + node;
+            if (ext) {
+                ok = node[j] >= 0 && node[j] < n_q;
+                if (node[j] >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, e * TN + s);
+                if (ok) rr = prefix + node[j];
             } else {
-                const int p = (e - nt_ext) * TN + s;
+                const int p = (e - nt_ext_of(count, a.ma)) * TN + s;
                 ok = p < prefix;
                 if (ok) rr = p;
             }
@@ -180,26 +213,20 @@ attn_mma_kernel(const AttnArgs a) {
         }
     };
     // without a prefix the first gathered tile is requested before the count has arrived
-    if (prefix == 0 || nt_gat > 0) load_gathered(0, 0, prefix == 0 || nt_ext > 0);
-    cp_async_commit();                                    // group 2
-    if (nt_gat > 1) load_gathered(1, 1, nt_ext > 1);
-    cp_async_commit();                                    // group 3
-
-    // ---- Q straight into A fragments; my two rows are r0 and r1 of the block
-    const int r0 = warp * 16 + g, r1 = r0 + 8;
-    const bool ok0 = row0 + r0 < n_q, ok1 = row0 + r1 < n_q;
-    uint32_t qf[KS][4];
-    {
-        const uint32_t *q0 = reinterpret_cast<const uint32_t *>(qp + (long long)(ok0 ? row0 + r0 : 0) * a.qs_n) + t;
-        const uint32_t *q1 = reinterpret_cast<const uint32_t *>(qp + (long long)(ok1 ? row0 + r1 : 0) * a.qs_n) + t;
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            qf[ks][0] = ok0 ? __ldg(q0 + ks * 8) : 0u;
-            qf[ks][1] = ok1 ? __ldg(q1 + ks * 8) : 0u;
-            qf[ks][2] = ok0 ? __ldg(q0 + ks * 8 + 4) : 0u;
-            qf[ks][3] = ok1 ? __ldg(q1 + ks * 8 + 4) : 0u;
-        }
+    if (prefix == 0) {
+        load_gathered(0, 0, true, nodeA);
+        cp_async_commit();                                // group 2
     }
+    const int nt_ext = nt_ext_of(count, a.ma);
+    const int nt_gat = nt_ext + (prefix + TN - 1) / TN;
+    if (prefix != 0) {
+        if (nt_gat > 0) load_gathered(0, 0, nt_ext > 0, nodeA);
+        cp_async_commit();                                // group 2
+    }
+    if (nt_gat > 1) load_gathered(1, 1, nt_ext > 1, nodeB);
+    cp_async_commit();                                    // group 3
+    fetch_idx(2, nodeA);
+    fetch_idx(3, nodeB);
 
     float acc[ND][4];
 #pragma unroll
@@ -208,27 +235,37 @@ attn_mma_kernel(const AttnArgs a) {
     const float c2 = a.scale_log2;
 
     const int n_tiles = NBLK + nt_gat;
+    // mask words of my two rows for column tile i (fetched one tile ahead of their use)
+    auto mask_words = [&](int i, uint32_t &w0, uint32_t &w1) {
+        w0 = w1 = 0u;
+        if (i < NBLK) {
+            if (ok0) w0 = __ldg(g_bmask + r0 * BW + i);
+            if (ok1) w1 = __ldg(g_bmask + r1 * BW + i);
+        } else if (i - NBLK < nt_ext) {
+            const int e = i - NBLK;
+            if (ok0 && e < maw) w0 = __ldg(g_emask + r0 * maw + e);
+            if (ok1 && e < maw) w1 = __ldg(g_emask + r1 * maw + e);
+        } else if (i < n_tiles) {
+            const int rem = prefix - (i - NBLK - nt_ext) * TN;
+            w0 = w1 = rem >= 32 ? 0xffffffffu : ((1u << rem) - 1u);
+        }
+    };
+    uint32_t w0n, w1n;
+    mask_words(0, w0n, w1n);
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < NBLK;
         const int e = i - NBLK;                           // gathered tile number
-        uint32_t kbase, vbase, w0, w1;
+        const uint32_t w0 = w0n, w1 = w1n;
+        mask_words(i + 1, w0n, w1n);
+        uint32_t kbase, vbase;
         if (blk) {
             kbase = s_base + SM::KB + i * TN * RS;
             vbase = s_base + SM::VB + i * TN * RS;
-            w0 = ok0 ? __ldg(g_bmask + r0 * BW + i) : 0u;
-            w1 = ok1 ? __ldg(g_bmask + r1 * BW + i) : 0u;
             if (i == 0) { cp_async_wait<3>(); __syncthreads(); }
         } else {
             kbase = s_base + SM::KE + (e & 1) * TN * RS;
             vbase = s_base + SM::VE + (e & 1) * TN * RS;
-            if (e < nt_ext) {
-                w0 = (ok0 && e < maw) ? __ldg(g_emask + r0 * maw + e) : 0u;
-                w1 = (ok1 && e < maw) ? __ldg(g_emask + r1 * maw + e) : 0u;
-            } else {
-                const int rem = prefix - (e - nt_ext) * TN;
-                w0 = w1 = rem >= 32 ? 0xffffffffu : ((1u << rem) - 1u);
-            }
             cp_async_wait<1>();
             __syncthreads();
         }
@@ -321,7 +358,13 @@ attn_mma_kernel(const AttnArgs a) {
         if (!blk) {                                       // recycle this stage for tile e + 2
             if (e + 2 < nt_gat) {
                 __syncthreads();
-                load_gathered(e + 2, e & 1, e + 2 < nt_ext);
+                if (e & 1) {
+                    load_gathered(e + 2, 1, e + 2 < nt_ext, nodeB);
+                    fetch_idx(e + 4, nodeB);
+                } else {
+                    load_gathered(e + 2, 0, e + 2 < nt_ext, nodeA);
+                    fetch_idx(e + 4, nodeA);
+                }
             }
             cp_async_commit();
         }
