@@ -71,6 +71,7 @@ const char *fst_status_string(int s) {
         case FST_DEV_MALFORMED_TREE: return "malformed tree: parent[i] must be -1 or an earlier node";
         case FST_DEV_ANCESTOR_OVERFLOW: return "a block has more unique ancestors than max_ancestors";
         case FST_DEV_INDEX_RANGE: return "metadata index outside the K/V rows";
+        case FST_DEV_TIMEOUT: return "a bounded wait on an asynchronous copy ran out";
         default: return "unknown status";
     }
 }
@@ -158,14 +159,17 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
         if ((s * es) & 15) rows_aligned = false;
 
     int choice = kernel;
-    if (choice == FST_KERNEL_AUTO)
-        choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_MMA
-                                                                    : FST_KERNEL_SIMT;
+    const bool automatic = choice == FST_KERNEL_AUTO;
+    if (automatic)
+        choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_TMA : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice != FST_KERNEL_MMA) return FST_ERR_INVALID_ARG;
+    if (choice != FST_KERNEL_MMA && choice != FST_KERNEL_TMA) return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
-    return cuda_status(launch_attention_mma(a, dtype, 0, st));
+    cudaError_t e = launch_attention_mma(a, dtype, choice, st);
+    // shapes or strides the TMA variant cannot describe fall back to the cp.async variant
+    if (e == cudaErrorNotSupported && automatic) e = launch_attention_mma(a, dtype, FST_KERNEL_MMA, st);
+    return cuda_status(e);
 }
 
 size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m, int max_ancestors) {

@@ -1,0 +1,449 @@
+// Tree attention, TMA variant: the same mathematics and tile structure as attn_mma_kernel
+// (fst_attention_mma.cuh; reference fstattention.py:21-151), with the contiguous operands moved
+// by the tensor memory accelerator instead of the load/store unit.
+//
+// Why: with 16-byte cp.async copies and 4-byte Q accesses the LSU data pipe is the busiest
+// unit of the SM (about 3000 wavefronts per 64-row block, 58 % busy at 3 CTAs/SM, a third of
+// them Q fragment loads) and sits on the critical path of the prologue.  Here
+//   * Q and the block's own K and V rows are 32-row x 64-column boxes fetched with
+//     cp.async.bulk.tensor (one thread issues them; rows past the end of the tensor arrive as
+//     zeros) and complete on mbarriers;
+//   * every tile lives in shared memory in the 128-byte-swizzled layout TMA writes (16-byte
+//     chunk c of row r sits at chunk c ^ (r & 7)), which makes ldmatrix conflict free without
+//     padding; the gathered ancestor rows are placed into the same layout by cp.async;
+//   * Q is read with ldmatrix; its buffer doubles as the second gathered stage.
+//
+// Every mbarrier wait is bounded in time: when it runs out the kernel records FST_DEV_TIMEOUT in
+// the status record and carries on to its exit instead of spinning.
+
+#pragma once
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "fst_attention_mma.cuh"
+
+namespace fst {
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+// Wait for a phase, but never longer than ~50 ms: on giving up the status record gets
+// FST_DEV_TIMEOUT and the caller carries on to its exit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t *status, int where) {
+    if (mbar_test(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+#pragma unroll 1
+    for (int it = 0; it < (1 << 24); ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 15) == 15 && global_ns() - t0 > 50000000ull) break;
+    }
+    report(status, FST_DEV_TIMEOUT, where, int(parity));
+    return false;
+}
+// one box of a rank-4 tensor (columns, rows, head, batch) into shared memory
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                            int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%2, %3, %4, %5}], [%6];\n"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
+// A tile is 32 rows; with D = 128 it is two 4 KB halves (columns 0-63, 64-127), each 32 rows of
+// 128 bytes in the swizzled layout.
+template <int D>
+struct SwzTile {
+    static constexpr int HALVES = D / 64;
+    static constexpr int BYTES = 32 * D * 2;
+    // byte offset of 16-byte chunk `c` (0 .. D/8-1) of row `r` (0..31)
+    __device__ static __forceinline__ uint32_t off(int r, int c) {
+        return uint32_t((c >> 3) * 4096 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+    }
+};
+
+template <int D, int BM>
+struct TmaSmem {
+    static constexpr int TILE = SwzTile<D>::BYTES;
+    static constexpr int NB32 = (BM + 31) / 32;           // 32-row tiles per block
+    static constexpr int KB = 0;                          // the block's own K rows
+    static constexpr int VB = KB + NB32 * TILE;
+    static constexpr int ST0 = VB + NB32 * TILE;          // stage 0: one K tile then one V tile
+    static constexpr int ST1 = ST0 + 2 * TILE;            // stage 1, shared with the Q tiles
+    static constexpr int QO = ST1;
+    static constexpr int QO_TILES = NB32 > 2 ? NB32 : 2;
+    static constexpr int BAR = QO + QO_TILES * TILE;      // two mbarriers
+    static constexpr int BYTES = BAR + 64 + 1024;         // + slack to align the base to 1 KB
+};
+
+template <typename T, int D, int BM>
+__global__ void __launch_bounds__(BM * 2, (BM <= 64 ? 3 : 1))
+attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    using MT = MmaTraits<T>;
+    using SM = TmaSmem<D, BM>;
+    using TL = SwzTile<D>;
+    constexpr int TN = MMA_TN;
+    constexpr int NT = BM * 2;            // threads
+    constexpr int CH = D / 8;             // 16-byte chunks per row
+    constexpr int KS = D / 16;
+    constexpr int ND = D / 8;
+    constexpr int RPP = NT / CH;          // rows covered by one pass of all threads
+    constexpr int SPT = TN / RPP;         // gathered rows per thread and tile
+    constexpr int NBLK = SM::NB32;
+    constexpr int BW = (BM + 31) / 32;
+    static_assert(NT % CH == 0 && TN % RPP == 0, "thread count must cover whole rows and tiles");
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;    // swizzle atoms are 1 KB
+    const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = b * BM;
+    const int prefix = a.prefix, n_q = a.n_q;
+    const uint32_t bar_qk = s_base + SM::BAR, bar_v = bar_qk + 8;
+
+    const PackedLayout L = packed_layout(a.nb, BM, a.ma);
+    const int maw = L.maw;
+    const unsigned char *blob = a.packed + size_t(z) * a.meta_stride;
+    const int32_t *g_idx = reinterpret_cast<const int32_t *>(blob + L.off_idx) + size_t(b) * a.ma;
+    const uint32_t *g_emask = reinterpret_cast<const uint32_t *>(blob + L.off_emask) + size_t(b) * BM * maw;
+    const uint32_t *g_bmask = reinterpret_cast<const uint32_t *>(blob + L.off_bmask) + size_t(b) * BM * BW;
+    const int count = __ldg(reinterpret_cast<const int32_t *>(blob + L.off_count) + b);
+
+    const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
+    const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + h * a.vs_h;
+    T *op = static_cast<T *>(a.o) + z * a.os_z + h * a.os_h;
+
+    const int lr = tid / CH, lc = tid % CH;               // my row-in-pass and 16-byte chunk
+    const int r0 = warp * 16 + g, r1 = r0 + 8;            // my two rows inside the block
+    const bool ok0 = row0 + r0 < n_q, ok1 = row0 + r1 < n_q;
+
+    int nodeA[SPT], nodeB[SPT];                           // my slots of the next two external tiles
+    auto fetch_idx = [&](int e, int (&node)[SPT]) {       // the index list is -1 padded
+#pragma unroll
+        for (int j = 0; j < SPT; ++j) {
+            const int slot = e * TN + lr + j * RPP;
+            node[j] = slot < a.ma ? __ldg(g_idx + slot) : -1;
+        }
+    };
+    fetch_idx(0, nodeA);
+    fetch_idx(1, nodeB);
+
+    // ---- one thread starts the TMA transfers: Q and block K on one barrier, block V on another
+    if (tid == 0) {
+        mbar_init(bar_qk, 1);
+        mbar_init(bar_v, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        mbar_arrive_expect_tx(bar_qk, 2 * NBLK * SM::TILE);
+#pragma unroll
+        for (int j = 0; j < NBLK; ++j)
+#pragma unroll
+            for (int hf = 0; hf < TL::HALVES; ++hf) {
+                tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, h, z, bar_qk);
+                tma_load_4d(s_base + SM::QO + j * SM::TILE + hf * 4096, &tm_q, hf * 64, row0 + j * 32, h, z, bar_qk);
+            }
+        mbar_arrive_expect_tx(bar_v, NBLK * SM::TILE);
+#pragma unroll
+        for (int j = 0; j < NBLK; ++j)
+#pragma unroll
+            for (int hf = 0; hf < TL::HALVES; ++hf)
+                tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, h, z, bar_v);
+    }
+
+    // ---- gathered tiles (cp.async into the swizzled layout): external ancestors, then prefix
+    auto load_gathered = [&](int e, int st, bool ext, const int (&node)[SPT]) {
+        const uint32_t kd = s_base + (st ? SM::ST1 : SM::ST0);
+        const uint32_t vd = kd + SM::TILE;
+#pragma unroll
+        for (int j = 0; j < SPT; ++j) {
+            const int s = lr + j * RPP;
+            long long rr = 0;
+            bool ok;
+            if (ext) {
+                ok = node[j] >= 0 && node[j] < n_q;
+                if (node[j] >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, e * TN + s);
+                if (ok) rr = prefix + node[j];
+            } else {
+                const int p = (e - nt_ext_of(count, a.ma)) * TN + s;
+                ok = p < prefix;
+                if (ok) rr = p;
+            }
+            const uint32_t o = TL::off(s, lc);
+            cp_async16(kd + o, kp + rr * a.ks_n + lc * 8, ok);
+            cp_async16(vd + o, vp + rr * a.vs_n + lc * 8, ok);
+        }
+    };
+    // without a prefix the first gathered tile is requested before the count has arrived
+    if (prefix == 0) {
+        load_gathered(0, 0, true, nodeA);
+        cp_async_commit();                                // group 0
+    }
+    const int nt_ext = nt_ext_of(count, a.ma);
+    const int nt_gat = nt_ext + (prefix + TN - 1) / TN;
+    if (prefix != 0) {
+        if (nt_gat > 0) load_gathered(0, 0, nt_ext > 0, nodeA);
+        cp_async_commit();                                // group 0
+    }
+    fetch_idx(2, nodeA);
+
+    // ---- Q fragments; afterwards stage 1, which shares Q's memory, may be filled
+    __syncthreads();                                      // barrier initialisation is visible
+    bool alive = mbar_wait(bar_qk, 0, a.status, b);
+    uint32_t qf[KS][4];
+    {
+        const int qr = warp * 16 + (lane & 15);           // row of the block this lane addresses
+        const uint32_t qb = s_base + SM::QO + (qr >> 5) * SM::TILE;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], qb + TL::off(qr & 31, ks * 2 + (lane >> 4)));
+    }
+    if (nt_gat > 1) {
+        __syncthreads();
+        load_gathered(1, 1, nt_ext > 1, nodeB);
+    }
+    cp_async_commit();                                    // group 1
+    fetch_idx(3, nodeB);
+
+    float acc[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // m in raw score units; l is my share
+    const float c2 = a.scale_log2;
+
+    const int n_tiles = NBLK + nt_gat;
+    auto mask_words = [&](int i, uint32_t &w0, uint32_t &w1) {
+        w0 = w1 = 0u;
+        if (i < NBLK) {
+            if (ok0) w0 = __ldg(g_bmask + r0 * BW + i);
+            if (ok1) w1 = __ldg(g_bmask + r1 * BW + i);
+        } else if (i - NBLK < nt_ext) {
+            const int e = i - NBLK;
+            if (ok0 && e < maw) w0 = __ldg(g_emask + r0 * maw + e);
+            if (ok1 && e < maw) w1 = __ldg(g_emask + r1 * maw + e);
+        } else if (i < n_tiles) {
+            const int rem = prefix - (i - NBLK - nt_ext) * TN;
+            w0 = w1 = rem >= 32 ? 0xffffffffu : ((1u << rem) - 1u);
+        }
+    };
+    uint32_t w0n, w1n;
+    mask_words(0, w0n, w1n);
+#pragma unroll 1
+    for (int i = 0; i < n_tiles; ++i) {
+        const bool blk = i < NBLK;
+        const int e = i - NBLK;                           // gathered tile number
+        const uint32_t w0 = w0n, w1 = w1n;
+        mask_words(i + 1, w0n, w1n);
+        uint32_t kbase, vbase;
+        if (blk) {
+            kbase = s_base + SM::KB + i * SM::TILE;
+            vbase = s_base + SM::VB + i * SM::TILE;
+        } else {
+            kbase = s_base + ((e & 1) ? SM::ST1 : SM::ST0);
+            vbase = kbase + SM::TILE;
+            cp_async_wait<1>();
+            __syncthreads();
+        }
+        const uint32_t occ = __reduce_or_sync(0xffffffffu, w0 | w1);   // columns any of my 16 rows use
+        const bool lo = (occ & 0xffffu) != 0u, hi = (occ >> 16) != 0u;
+
+        uint32_t pf[2][4];
+        if (occ) {
+            float s[4][4];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            const int krow = ((lane >> 4) << 3) + (lane & 7), kch = (lane >> 3) & 1;
+#pragma unroll
+            for (int cg = 0; cg < 2; ++cg) {
+                if (cg == 0 ? lo : hi) {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        uint32_t kb[4];
+                        ldmatrix_x4(kb, kbase + TL::off(cg * 16 + krow, ks * 2 + kch));
+                        MT::mma(s[2 * cg], qf[ks], kb[0], kb[1]);
+                        MT::mma(s[2 * cg + 1], qf[ks], kb[2], kb[3]);
+                    }
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                if (n < 2 ? lo : hi) {
+                    const int c = n * 8 + 2 * t;
+                    s[n][0] = ((w0 >> c) & 1u) ? s[n][0] : -INFINITY;
+                    s[n][1] = ((w0 >> c) & 2u) ? s[n][1] : -INFINITY;
+                    s[n][2] = ((w1 >> c) & 1u) ? s[n][2] : -INFINITY;
+                    s[n][3] = ((w1 >> c) & 2u) ? s[n][3] : -INFINITY;
+                    mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+                    mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float mu0 = mn0 == -INFINITY ? 0.f : mn0 * c2, mu1 = mn1 == -INFINITY ? 0.f : mn1 * c2;
+            const float al0 = fast_exp2(m0 * c2 - mu0), al1 = fast_exp2(m1 * c2 - mu1);
+            m0 = mn0; m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                if (n < 2 ? lo : hi) {
+                    const float p0 = fast_exp2(fmaf(s[n][0], c2, -mu0)), p1 = fast_exp2(fmaf(s[n][1], c2, -mu0));
+                    const float p2 = fast_exp2(fmaf(s[n][2], c2, -mu1)), p3 = fast_exp2(fmaf(s[n][3], c2, -mu1));
+                    ps0 += p0 + p1;
+                    ps1 += p2 + p3;
+                    pf[n >> 1][(n & 1) * 2 + 0] = MT::pack(p0, p1);
+                    pf[n >> 1][(n & 1) * 2 + 1] = MT::pack(p2, p3);
+                }
+            }
+            l0 = l0 * al0 + ps0;
+            l1 = l1 * al1 + ps1;
+            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+                for (int d = 0; d < ND; ++d) {
+                    acc[d][0] *= al0; acc[d][1] *= al0;
+                    acc[d][2] *= al1; acc[d][3] *= al1;
+                }
+            }
+        }
+
+        if (blk && i == 0) alive = mbar_wait(bar_v, 0, a.status, b) && alive;   // the block's V rows
+
+        if (occ) {
+            const int vrow = (((lane >> 3) & 1) << 3) + (lane & 7), vch = lane >> 4;
+#pragma unroll
+            for (int cg = 0; cg < 2; ++cg) {
+                if (cg == 0 ? lo : hi) {
+#pragma unroll
+                    for (int dp = 0; dp < ND / 2; ++dp) {
+                        uint32_t vb[4];
+                        ldmatrix_x4_trans(vb, vbase + TL::off(cg * 16 + vrow, dp * 2 + vch));
+                        MT::mma(acc[2 * dp], pf[cg], vb[0], vb[1]);
+                        MT::mma(acc[2 * dp + 1], pf[cg], vb[2], vb[3]);
+                    }
+                }
+            }
+        }
+
+        if (!blk) {                                       // recycle this stage for tile e + 2
+            if (e + 2 < nt_gat) {
+                __syncthreads();
+                if (e & 1) {
+                    load_gathered(e + 2, 1, e + 2 < nt_ext, nodeB);
+                    fetch_idx(e + 4, nodeB);
+                } else {
+                    load_gathered(e + 2, 0, e + 2 < nt_ext, nodeA);
+                    fetch_idx(e + 4, nodeA);
+                }
+            }
+            cp_async_commit();
+        }
+    }
+
+    // ---- epilogue: normalise and store each quad's 16-byte pieces directly
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = (l0 > 0.f && alive) ? 1.f / l0 : 0.f, inv1 = (l1 > 0.f && alive) ? 1.f / l1 : 0.f;
+    if (ok0) {
+        uint32_t *o0 = reinterpret_cast<uint32_t *>(op + (long long)(row0 + r0) * a.os_n) + t;
+#pragma unroll
+        for (int d = 0; d < ND; ++d) o0[d * 4] = MT::pack(acc[d][0] * inv0, acc[d][1] * inv0);
+    }
+    if (ok1) {
+        uint32_t *o1 = reinterpret_cast<uint32_t *>(op + (long long)(row0 + r1) * a.os_n) + t;
+#pragma unroll
+        for (int d = 0; d < ND; ++d) o1[d * 4] = MT::pack(acc[d][2] * inv1, acc[d][3] * inv1);
+    }
+    if (a.lse != nullptr && t == 0) {
+        float *lse = a.lse + (size_t(z) * a.H + h) * n_q;
+        if (ok0) lse[row0 + r0] = m0 * c2 + log2f(l0);
+        if (ok1) lse[row0 + r1] = m1 * c2 + log2f(l1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side: tensor maps and launch
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// rank-4 map (columns, rows, heads, batch) with 64-column x 32-row boxes, 128-byte swizzle
+inline bool make_map(CUtensorMap *map, const void *base, bool bf16, int D, int rows, int H, int Z,
+                     int64_t stride_n, int64_t stride_h, int64_t stride_z) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
+    const cuuint64_t strides[3] = {cuuint64_t(stride_n) * 2, cuuint64_t(stride_h) * 2, cuuint64_t(stride_z) * 2};
+    const cuuint32_t box[4] = {64, 32, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int D, int BM>
+cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
+    using SM = TmaSmem<D, BM>;
+    constexpr size_t smem = SM::BYTES;
+    constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+    // a dimension of size 1 may carry any stride; TMA wants strides that grow with the dimension
+    alignas(64) CUtensorMap tq, tk, tv;
+    if (!make_map(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
+        !make_map(&tk, a.k, bf16, D, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z))
+        return cudaErrorNotSupported;
+    static bool configured = false;                       // one process drives one device
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
+    attn_tma_kernel<T, D, BM><<<grid, block, smem, stream>>>(a, tq, tk, tv);
+    return cudaGetLastError();
+}
+
+template <typename T, int D>
+cudaError_t launch_tma_d(const AttnArgs &a, cudaStream_t stream) {
+    switch (a.bm) {
+        case 32: return launch_tma_inst<T, D, 32>(a, stream);
+        case 64: return launch_tma_inst<T, D, 64>(a, stream);
+        case 128: return launch_tma_inst<T, D, 128>(a, stream);
+    }
+    return cudaErrorNotSupported;
+}
+
+}  // namespace fst

@@ -37,7 +37,8 @@ enum fst_status {
     FST_DEV_MALFORMED_TREE = 16,   /* parent[i] >= i or < -1; status[1] = node                  */
     FST_DEV_ANCESTOR_OVERFLOW = 17,/* a block has more unique ancestors than max_ancestors;     */
                                    /* status[1] = tree*65536+block, status[2] = the count        */
-    FST_DEV_INDEX_RANGE = 18       /* a metadata index points outside the K/V rows              */
+    FST_DEV_INDEX_RANGE = 18,      /* a metadata index points outside the K/V rows              */
+    FST_DEV_TIMEOUT = 19           /* a bounded wait on an asynchronous copy ran out            */
 };
 
 enum fst_dtype { FST_F16 = 0, FST_BF16 = 1, FST_F32 = 2 };
@@ -46,7 +47,8 @@ enum fst_dtype { FST_F16 = 0, FST_BF16 = 1, FST_F32 = 2 };
 enum fst_kernel {
     FST_KERNEL_AUTO = 0,
     FST_KERNEL_SIMT = 1,           /* fp32 arithmetic, any dtype / head_dim in {16,32,64,128}   */
-    FST_KERNEL_MMA = 2             /* tensor-core kernel: fp16/bf16, head_dim 64/128            */
+    FST_KERNEL_MMA = 2,            /* tensor-core kernel, cp.async gathers: fp16/bf16, D 64/128  */
+    FST_KERNEL_TMA = 3             /* same arithmetic, bulk-copy-engine transfers + mbarriers    */
 };
 
 int fst_version(void);
