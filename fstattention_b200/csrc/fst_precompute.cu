@@ -6,9 +6,11 @@
 //   leaf  = rows of the block that are not in A_b, rows past the last node
 //           included                                                           (utils.py:121-122)
 // The reference gets there with unique / isin over a lineage matrix in Python loops; here one
-// CTA per (tree, block) marks ancestors in a shared-memory bitmap by walking parent links,
-// ranks the set bits with a popcount prefix scan (which yields the ascending order of
-// torch.unique without sorting) and walks each row's chain once more to set its mask bits.
+// CTA per (tree, block) marks ancestors by walking parent links (byte flags in shared memory,
+// plain stores: many walkers hit the same few nodes and atomics on one word would serialise),
+// packs the flags into a bitmap, ranks the set bits with a popcount prefix scan (which yields
+// the ascending order of torch.unique without sorting) and walks each row's chain once more to
+// set its mask bits.
 // Integer work only; the reference-format outputs are bit-identical to the reference's.
 //
 // The packed form written for the attention kernels splits A_b in two: ancestors outside the
@@ -29,7 +31,7 @@ constexpr int PRE_THREADS = 256;
 constexpr int PRE_WARPS = PRE_THREADS / 32;
 
 __global__ void __launch_bounds__(PRE_THREADS)
-precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, int ma, int par_cap,
+precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, int ma, int par_cap, int depth_cap,
                   int64_t *__restrict__ anc_idx_all, uint8_t *__restrict__ anc_mask_all,
                   int64_t *__restrict__ leaf_idx_all, unsigned char *__restrict__ packed_all,
                   size_t packed_stride, int32_t *status) {
@@ -48,43 +50,59 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     uint32_t *rowmask = reinterpret_cast<uint32_t *>(rank + W);      // [bm][maw] over all of A_b
     uint32_t *blkmask = rowmask + size_t(bm) * maw;                   // [bm][bw] over block rows
     int *warp_tot = reinterpret_cast<int *>(blkmask + size_t(bm) * bw);
-    int *s_par = warp_tot + 40;
+    unsigned char *flag = reinterpret_cast<unsigned char *>(warp_tot + 40);   // [W*32] node is an ancestor
+    int *chain = reinterpret_cast<int *>(flag + size_t(W) * 32);      // [depth_cap][bm] ancestors of row j
+    int *depth = chain + size_t(depth_cap) * bm;                      // [bm] recorded chain length
+    int *s_par = depth + bm;
 
     const int32_t *parent = parent_all + size_t(tree) * n_nodes;
     const int cap = min(par_cap, n_here);
-    for (int i = tid; i < cap; i += PRE_THREADS) s_par[i] = parent[i];
-    for (int i = tid; i < W; i += PRE_THREADS) bitmap[i] = 0u;
-    for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
-    for (int i = tid; i < bm * bw; i += PRE_THREADS) blkmask[i] = 0u;
-    __syncthreads();
-
-    // parent of x; a malformed entry is reported and treated as a root, so every walk ends
-    auto par = [&](int x) -> int {
-        int p = x < cap ? s_par[x] : __ldg(parent + x);
+    // parents are checked once, here: a malformed entry is reported and treated as a root, so
+    // every walk below ends
+    auto checked = [&](int x, int p) -> int {
         if (p >= x || p < -1) {
             report(status, FST_DEV_MALFORMED_TREE, x, p);
             p = -1;
         }
         return p;
     };
+    for (int i = tid; i < cap; i += PRE_THREADS) s_par[i] = checked(i, parent[i]);
+    for (int i = tid; i < W * 8; i += PRE_THREADS) reinterpret_cast<uint32_t *>(flag)[i] = 0u;
+    for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
+    for (int i = tid; i < bm * bw; i += PRE_THREADS) blkmask[i] = 0u;
+    __syncthreads();
 
-    // 1. mark every strict ancestor of the block's rows.  A walker that sees a bit already set
-    //    stops: whoever set it keeps climbing, so everything above is (or will be) marked.  The
-    //    test is a plain read (a stale 0 only costs a redundant climb) and the set is a
-    //    fire-and-forget atomic, so a step costs one shared-memory round trip.
+    const bool all_staged = cap >= n_here;
+    auto par = [&](int x) -> int {
+        if (all_staged || x < cap) return s_par[x];
+        return checked(x, __ldg(parent + x));
+    };
+
+    // 1. every row climbs to its root, recording the chain (its lineage) and flagging each node
+    //    as an ancestor.  Flags are bytes written with plain stores: many rows hit the same few
+    //    nodes and atomics on one word would serialise.  The loop body is kept minimal because
+    //    its length times the depth of the tree is the critical path of this kernel.
+    int too_deep = 0;
     for (int j = tid; j < bm; j += PRE_THREADS) {
         const int k = row0 + j;
+        int n = 0;
         if (k < n_nodes) {
             int a = par(k);
             while (a >= 0) {
-                const uint32_t bit = 1u << (a & 31);
-                const uint32_t seen = *reinterpret_cast<volatile uint32_t *>(&bitmap[a >> 5]);
-                const int up = par(a);
-                if (seen & bit) break;
-                atomicOr(&bitmap[a >> 5], bit);
-                a = up;
+                if (n < depth_cap) chain[n * bm + j] = a;
+                flag[a] = 1;
+                ++n;
+                a = par(a);
             }
         }
+        depth[j] = n;
+        too_deep |= n > depth_cap;
+    }
+    const bool walk_masks = __syncthreads_or(too_deep) != 0;          // also: flags complete
+    // flags -> bitmap, one warp per word
+    for (int w = wid; w < W; w += PRE_WARPS) {
+        const uint32_t word = __ballot_sync(0xffffffffu, flag[w * 32 + lane] != 0);
+        if (lane == 0) bitmap[w] = word;
     }
     __syncthreads();
 
@@ -140,19 +158,16 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     uint8_t *o_mask = anc_mask_all ? anc_mask_all + blk * size_t(bm) * ma : nullptr;
     int64_t *o_leaf = leaf_idx_all ? leaf_idx_all + blk * bm : nullptr;
 
-    // 3. ascending ancestor list: slot = rank of the bit
-    for (int w = tid; w < W; w += PRE_THREADS) {
-        uint32_t bits = bitmap[w];
-        int pos = rank[w];
-        while (bits) {
-            const int bit = __ffs(bits) - 1;
-            bits &= bits - 1;
+    // 3. ascending ancestor list: slot = rank of the bit; one warp per word, one lane per node
+    for (int w = wid; w < W; w += PRE_WARPS) {
+        const uint32_t bits = bitmap[w];
+        if ((bits >> lane) & 1u) {
+            const int pos = rank[w] + __popc(bits & ((1u << lane) - 1u));
             if (pos < ma) {
-                const int node = w * 32 + bit;
+                const int node = w * 32 + lane;
                 if (p_idx && node < row0) p_idx[pos] = node;
                 if (o_idx) o_idx[pos] = node;
             }
-            ++pos;
         }
     }
     if (p_idx)
@@ -161,22 +176,50 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
         for (int a = n_keep + tid; a < ma; a += PRE_THREADS) o_idx[a] = -1;
     if (tid == 0 && p_count) p_count[b] = n_ext;
 
-    // 4. mask rows: the node itself (when it is somebody's ancestor in this block) and its chain
-    for (int j = tid; j < bm; j += PRE_THREADS) {
-        const int k = row0 + j;
-        blkmask[j * bw + (j >> 5)] |= 1u << (j & 31);     // every row attends to itself
-        if (k < n_nodes) {
-            int x = k;
-            while (x >= 0) {
+    // 4. mask rows: bit (row, slot of node) for the row itself, when it is somebody's ancestor
+    //    here, and for every node of its chain; plus the same in block-column space.
+    if (!walk_masks) {
+        // one work item per recorded (row, chain step), spread over all threads
+        for (int j = tid; j < bm; j += PRE_THREADS) {
+            const int k = row0 + j;
+            atomicOr(&blkmask[j * bw + (j >> 5)], 1u << (j & 31));     // every row attends to itself
+            if (k < n_nodes && ((bitmap[k >> 5] >> (k & 31)) & 1u)) {
+                const int pos = rank[k >> 5] + __popc(bitmap[k >> 5] & ((1u << (k & 31)) - 1u));
+                if (pos < ma) atomicOr(&rowmask[j * maw + (pos >> 5)], 1u << (pos & 31));
+            }
+        }
+        int dmax = 0;
+        for (int j = lane; j < bm; j += 32) dmax = max(dmax, depth[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dmax = max(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
+        for (int i = tid; i < dmax * bm; i += PRE_THREADS) {
+            const int sidx = i / bm, j = i - sidx * bm;
+            if (sidx < depth[j]) {
+                const int x = chain[i];
                 const uint32_t word = bitmap[x >> 5];
-                const uint32_t bit = 1u << (x & 31);
-                const int up = par(x);
-                if (word & bit) {
-                    const int pos = rank[x >> 5] + __popc(word & (bit - 1u));
-                    if (pos < ma) rowmask[j * maw + (pos >> 5)] |= 1u << (pos & 31);
-                    if (x >= row0) blkmask[j * bw + ((x - row0) >> 5)] |= 1u << ((x - row0) & 31);
+                const int pos = rank[x >> 5] + __popc(word & ((1u << (x & 31)) - 1u));
+                if (pos < ma) atomicOr(&rowmask[j * maw + (pos >> 5)], 1u << (pos & 31));
+                if (x >= row0) atomicOr(&blkmask[j * bw + ((x - row0) >> 5)], 1u << ((x - row0) & 31));
+            }
+        }
+    } else {
+        // a chain longer than the recording space: walk every row's chain again
+        for (int j = tid; j < bm; j += PRE_THREADS) {
+            const int k = row0 + j;
+            blkmask[j * bw + (j >> 5)] |= 1u << (j & 31);
+            if (k < n_nodes) {
+                int x = k;
+                while (x >= 0) {
+                    const uint32_t word = bitmap[x >> 5];
+                    const uint32_t bit = 1u << (x & 31);
+                    const int up = par(x);
+                    if (word & bit) {
+                        const int pos = rank[x >> 5] + __popc(word & (bit - 1u));
+                        if (pos < ma) rowmask[j * maw + (pos >> 5)] |= 1u << (pos & 31);
+                        if (x >= row0) blkmask[j * bw + ((x - row0) >> 5)] |= 1u << ((x - row0) & 31);
+                    }
+                    x = up;
                 }
-                x = up;
             }
         }
     }
@@ -320,7 +363,12 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
     const int nb = (n_nodes + bm - 1) / bm;
     const int maw = (ma + 31) / 32;
     const size_t W = (size_t(nb) * bm + 31) / 32;
-    const size_t fixed = (2 * W + size_t(bm) * maw + size_t(bm) * ((bm + 31) / 32) + 40) * 4;
+    // recording space for the rows' chains: as deep as 48 KB allows, at most 1024 levels
+    int depth_cap = int((48 * 1024) / (size_t(bm) * 4));
+    if (depth_cap > 1024) depth_cap = 1024;
+    if (depth_cap < 1) depth_cap = 1;
+    const size_t fixed = (2 * W + size_t(bm) * maw + size_t(bm) * ((bm + 31) / 32) + 40 + size_t(bm)) * 4 + W * 32 +
+                         size_t(depth_cap) * bm * 4;
     const size_t budget = 200 * 1024;
     if (fixed + 1024 > budget) return cudaErrorInvalidValue;
     const size_t cap = (budget - fixed) / 4;
@@ -334,7 +382,7 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
     }
     dim3 grid(nb, n_trees);
     precompute_kernel<<<grid, PRE_THREADS, smem, stream>>>(
-        parent, n_nodes, bm, ma, par_cap, anc_idx, anc_mask, leaf_idx,
+        parent, n_nodes, bm, ma, par_cap, depth_cap, anc_idx, anc_mask, leaf_idx,
         static_cast<unsigned char *>(packed), packed_stride, status);
     return cudaGetLastError();
 }
