@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--kernel", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shard", action="store_true",
+                    help="strong scaling: split the workload's trees or heads over the ranks and "
+                         "all-gather the outputs (NCCL) once per step")
     return ap.parse_args()
 
 
@@ -362,13 +365,116 @@ def run_ours(args, rank, world):
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
-                     "kernel": "attn_mma_kernel", "achieved_incl_q_o": (kv + info["q_o_bytes_per_call"]) / (launch_us * 1e-6) / 1e9,
+                     "kernel": "attn_tma_kernel" if args.kernel in ("auto", "tma") else f"attn_{args.kernel}_kernel", "achieved_incl_q_o": (kv + info["q_o_bytes_per_call"]) / (launch_us * 1e-6) / 1e9,
                      "frac_of_nominal_8000": achieved / 8000.0},
     }
     if e2e is not None:
         line["e2e"] = e2e
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+
+
+def run_sharded(args, rank, world):
+    """One problem split over the ranks (by tree or by head) + one all-gather of outputs per step."""
+    import fstattention_b200 as fst
+    from fstattention_b200 import configs, sharding
+    import torch.distributed as dist
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    w = configs.workload(args.workload)
+    if w.shard not in ("tree", "head"):
+        raise SystemExit(f"workload {w.name} has no shard axis")
+    info = describe(w, args.layers)
+    dtype = {"fp16": torch.float16, "fp32": torch.float32, "bf16": torch.bfloat16}[w.dtype]
+    T, H, N, D, L = len(w.trees), w.heads, w.n_nodes, w.head_dim, args.layers
+    n_units = T if w.shard == "tree" else H
+    lo, hi = sharding.shard_bounds(n_units, world, rank)
+    Tl, Hl = (hi - lo, H) if w.shard == "tree" else (T, hi - lo)
+    trees = w.trees[lo:hi] if w.shard == "tree" else w.trees
+
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    layers = [tuple(torch.randn((Tl, Hl, N, D), generator=g, device=dev, dtype=torch.float32).to(dtype)
+                    for _ in range(3)) for _ in range(L)]
+    # outputs of all layers of the step in one buffer so that one collective moves them
+    if w.shard == "tree":
+        out_local = torch.empty((L, Tl, Hl, N, D), device=dev, dtype=dtype)
+        out_full = torch.empty((world, L, Tl, Hl, N, D), device=dev, dtype=dtype)
+    else:
+        out_local = torch.empty((L, Tl, Hl, N, D), device=dev, dtype=dtype)
+        out_full = torch.empty((world, L, Tl, Hl, N, D), device=dev, dtype=dtype)
+    if n_units % world:
+        raise SystemExit("the sharded bench wants the unit count to divide evenly")
+    parent = torch.tensor(trees if len(trees) > 1 else trees[0], dtype=torch.int32, device=dev)
+    meta = fst.build_tree_metadata(parent, w.block_m, w.max_ancestors, reference_format=False)
+
+    def compute():
+        fst.build_tree_metadata(parent, w.block_m, w.max_ancestors, out=meta, check=False)
+        for i, (q, k, v) in enumerate(layers):
+            fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, out=out_local[i], kernel=args.kernel)
+
+    compute()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        compute()
+
+    def step():
+        graph.replay()
+        if world > 1:
+            dist.all_gather_into_tensor(out_full.view(-1), out_local.view(-1))
+
+    def timed(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms / reps
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_step = timed(step, args.steps)
+    clocks = sampler.stop()
+    ms_compute = timed(graph.replay, args.steps)
+    assert fst.last_status(dev) == 0
+    if rank != 0:
+        return
+    kv = info["gathered_kv_bytes_per_call"]
+    peak, peak_kind = measured_hbm_peak()
+    line = {
+        "metric": METRIC, "value": kv * L / (ms_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.dtype,
+        "data": "synthetic",
+        "config": {"workload": w.name, "trees": T, "nodes": N, "heads": H, "head_dim": D,
+                   "block_m": w.block_m, "max_ancestors": w.max_ancestors, "calls_per_step": L,
+                   "shard": w.shard, "units_per_rank": hi - lo,
+                   "step": "1 precompute + calls_per_step attention launches on the local shard (CUDA graph), "
+                           "then one NCCL all-gather of the step's outputs",
+                   "l2": f"{L} layer buffers per rank", "kernel": args.kernel},
+        "us_per_call": ms_step * 1e3 / L, "compute_only_us_per_call": ms_compute * 1e3 / L,
+        "all_gather_bytes_per_step": out_full.numel() * out_full.element_size(),
+        "gathered_kv_bytes_per_call": kv, "gpu_launches": args.steps * (L + 1), "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": kv / world / (ms_compute * 1e-3 / L) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": kv / world / (ms_compute * 1e-3 / L) / 1e9 / peak, "traffic": None,
+                     "peak_source": f"of {peak_kind}", "kernel": "attn_tma_kernel", "per": "GPU, compute only"},
+    }
     print(json.dumps(line))
 
 
@@ -410,7 +516,10 @@ def main():
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
         dist.init_process_group("nccl")
     try:
-        run_ours(args, rank, world)
+        if args.shard:
+            run_sharded(args, rank, world)
+        else:
+            run_ours(args, rank, world)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -66,7 +66,19 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
         }
         return p;
     };
-    for (int i = tid; i < cap; i += PRE_THREADS) s_par[i] = checked(i, parent[i]);
+    for (int i0 = tid; i0 < cap; i0 += 8 * PRE_THREADS) {    // eight loads in flight per thread
+        int v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * PRE_THREADS;
+            v[u] = i < cap ? __ldg(parent + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * PRE_THREADS;
+            if (i < cap) s_par[i] = checked(i, v[u]);
+        }
+    }
     for (int i = tid; i < W * 8; i += PRE_THREADS) reinterpret_cast<uint32_t *>(flag)[i] = 0u;
     for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
     for (int i = tid; i < bm * bw; i += PRE_THREADS) blkmask[i] = 0u;
