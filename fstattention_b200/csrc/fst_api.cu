@@ -163,7 +163,9 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
     if (automatic)
         choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_TMA : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice != FST_KERNEL_MMA && choice != FST_KERNEL_TMA) return FST_ERR_INVALID_ARG;
+    if (choice != FST_KERNEL_MMA && choice != FST_KERNEL_TMA && choice != FST_KERNEL_TMA_T32 &&
+        choice != FST_KERNEL_TMA_T64)
+        return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
     cudaError_t e = launch_attention_mma(a, dtype, choice, st);

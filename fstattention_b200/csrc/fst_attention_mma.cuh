@@ -90,8 +90,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int MMA_TN = 32;                                // K/V rows per column tile
 
+template <int TN = MMA_TN>
 __device__ __forceinline__ int nt_ext_of(int count, int ma) {   // external-ancestor tiles
-    return (min(max(count, 0), ma) + MMA_TN - 1) / MMA_TN;
+    return (min(max(count, 0), ma) + TN - 1) / TN;
 }
 
 template <int D, int BM>

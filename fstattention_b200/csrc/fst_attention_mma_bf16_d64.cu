@@ -3,7 +3,9 @@
 
 namespace fst {
 cudaError_t launch_mma_bf16_d64(const AttnArgs &a, int variant, cudaStream_t stream) {
-    if (variant == FST_KERNEL_TMA) return launch_tma_d<__nv_bfloat16, 64>(a, stream);
+    if (variant == FST_KERNEL_TMA) return launch_tma_d<__nv_bfloat16, 64>(a, 0, stream);
+    if (variant == FST_KERNEL_TMA_T32) return launch_tma_d<__nv_bfloat16, 64>(a, 32, stream);
+    if (variant == FST_KERNEL_TMA_T64) return launch_tma_d<__nv_bfloat16, 64>(a, 64, stream);
     return launch_mma_d<__nv_bfloat16, 64>(a, variant, stream);
 }
 }  // namespace fst

@@ -3,7 +3,9 @@
 
 namespace fst {
 cudaError_t launch_mma_f16_d128(const AttnArgs &a, int variant, cudaStream_t stream) {
-    if (variant == FST_KERNEL_TMA) return launch_tma_d<__half, 128>(a, stream);
+    if (variant == FST_KERNEL_TMA) return launch_tma_d<__half, 128>(a, 0, stream);
+    if (variant == FST_KERNEL_TMA_T32) return launch_tma_d<__half, 128>(a, 32, stream);
+    if (variant == FST_KERNEL_TMA_T64) return launch_tma_d<__half, 128>(a, 64, stream);
     return launch_mma_d<__half, 128>(a, variant, stream);
 }
 }  // namespace fst

@@ -76,35 +76,42 @@ struct SwzTile {
     }
 };
 
-template <int D, int BM>
+// Column tiles are TN = 32 or 64 K/V rows: 32 keeps three CTAs on an SM (the choice for large
+// grids), 64 halves the number of softmax rounds a warp runs one after the other (the choice when
+// the grid is too small to fill the machine and the latency of one CTA is what counts).
+template <int D, int BM, int TN>
 struct TmaSmem {
-    static constexpr int TILE = SwzTile<D>::BYTES;
-    static constexpr int NB32 = (BM + 31) / 32;           // 32-row tiles per block
+    static constexpr int TILE = SwzTile<D>::BYTES;        // one 32-row physical tile
+    static constexpr int NB32 = (BM + 31) / 32;           // physical tiles per block
+    static constexpr int TP = TN / 32;                    // physical tiles per column tile
+    static constexpr int NBT = (BM + TN - 1) / TN;        // column tiles holding the block's own rows
     static constexpr int KB = 0;                          // the block's own K rows
-    static constexpr int VB = KB + NB32 * TILE;
-    static constexpr int ST0 = VB + NB32 * TILE;          // stage 0: one K tile then one V tile
-    static constexpr int ST1 = ST0 + 2 * TILE;            // stage 1, shared with the Q tiles
+    static constexpr int VB = KB + NBT * TP * TILE;
+    static constexpr int ST0 = VB + NBT * TP * TILE;      // stage 0: one K column tile then one V
+    static constexpr int ST1 = ST0 + 2 * TP * TILE;       // stage 1, shared with the Q tiles
     static constexpr int QO = ST1;
-    static constexpr int QO_TILES = NB32 > 2 ? NB32 : 2;
+    static constexpr int QO_TILES = NB32 > 2 * TP ? NB32 : 2 * TP;
     static constexpr int BAR = QO + QO_TILES * TILE;      // two mbarriers
     static constexpr int BYTES = BAR + 64 + 1024;         // + slack to align the base to 1 KB
 };
 
-template <typename T, int D, int BM>
-__global__ void __launch_bounds__(BM * 2, (BM <= 64 ? 3 : 1))
+template <typename T, int D, int BM, int TN>
+__global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : 1))
 attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
     using MT = MmaTraits<T>;
-    using SM = TmaSmem<D, BM>;
+    using SM = TmaSmem<D, BM, TN>;
     using TL = SwzTile<D>;
-    constexpr int TN = MMA_TN;
     constexpr int NT = BM * 2;            // threads
     constexpr int CH = D / 8;             // 16-byte chunks per row
     constexpr int KS = D / 16;
     constexpr int ND = D / 8;
     constexpr int RPP = NT / CH;          // rows covered by one pass of all threads
     constexpr int SPT = TN / RPP;         // gathered rows per thread and tile
-    constexpr int NBLK = SM::NB32;
+    constexpr int NB32 = SM::NB32;
+    constexpr int NBLK = SM::NBT;
+    constexpr int TP = SM::TP;            // 32-row physical tiles (= mask words) per column tile
+    constexpr int NG = TN / 16;           // 16-column groups per column tile
     constexpr int BW = (BM + 31) / 32;
     static_assert(NT % CH == 0 && TN % RPP == 0, "thread count must cover whole rows and tiles");
 
@@ -149,17 +156,17 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         mbar_init(bar_qk, 1);
         mbar_init(bar_v, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        mbar_arrive_expect_tx(bar_qk, 2 * NBLK * SM::TILE);
+        mbar_arrive_expect_tx(bar_qk, 2 * NB32 * SM::TILE);
 #pragma unroll
-        for (int j = 0; j < NBLK; ++j)
+        for (int j = 0; j < NB32; ++j)
 #pragma unroll
             for (int hf = 0; hf < TL::HALVES; ++hf) {
                 tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, h, z, bar_qk);
                 tma_load_4d(s_base + SM::QO + j * SM::TILE + hf * 4096, &tm_q, hf * 64, row0 + j * 32, h, z, bar_qk);
             }
-        mbar_arrive_expect_tx(bar_v, NBLK * SM::TILE);
+        mbar_arrive_expect_tx(bar_v, NB32 * SM::TILE);
 #pragma unroll
-        for (int j = 0; j < NBLK; ++j)
+        for (int j = 0; j < NB32; ++j)
 #pragma unroll
             for (int hf = 0; hf < TL::HALVES; ++hf)
                 tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, h, z, bar_v);
@@ -168,7 +175,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     // ---- gathered tiles (cp.async into the swizzled layout): external ancestors, then prefix
     auto load_gathered = [&](int e, int st, bool ext, const int (&node)[SPT]) {
         const uint32_t kd = s_base + (st ? SM::ST1 : SM::ST0);
-        const uint32_t vd = kd + SM::TILE;
+        const uint32_t vd = kd + TP * SM::TILE;
 #pragma unroll
         for (int j = 0; j < SPT; ++j) {
             const int s = lr + j * RPP;
@@ -179,11 +186,11 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 if (node[j] >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, e * TN + s);
                 if (ok) rr = prefix + node[j];
             } else {
-                const int p = (e - nt_ext_of(count, a.ma)) * TN + s;
+                const int p = (e - nt_ext_of<TN>(count, a.ma)) * TN + s;
                 ok = p < prefix;
                 if (ok) rr = p;
             }
-            const uint32_t o = TL::off(s, lc);
+            const uint32_t o = (s >> 5) * SM::TILE + TL::off(s & 31, lc);
             cp_async16(kd + o, kp + rr * a.ks_n + lc * 8, ok);
             cp_async16(vd + o, vp + rr * a.vs_n + lc * 8, ok);
         }
@@ -193,7 +200,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         load_gathered(0, 0, true, nodeA);
         cp_async_commit();                                // group 0
     }
-    const int nt_ext = nt_ext_of(count, a.ma);
+    const int nt_ext = nt_ext_of<TN>(count, a.ma);
     const int nt_gat = nt_ext + (prefix + TN - 1) / TN;
     if (prefix != 0) {
         if (nt_gat > 0) load_gathered(0, 0, nt_ext > 0, nodeA);
@@ -225,68 +232,86 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     const float c2 = a.scale_log2;
 
     const int n_tiles = NBLK + nt_gat;
-    auto mask_words = [&](int i, uint32_t &w0, uint32_t &w1) {
-        w0 = w1 = 0u;
-        if (i < NBLK) {
-            if (ok0) w0 = __ldg(g_bmask + r0 * BW + i);
-            if (ok1) w1 = __ldg(g_bmask + r1 * BW + i);
-        } else if (i - NBLK < nt_ext) {
-            const int e = i - NBLK;
-            if (ok0 && e < maw) w0 = __ldg(g_emask + r0 * maw + e);
-            if (ok1 && e < maw) w1 = __ldg(g_emask + r1 * maw + e);
-        } else if (i < n_tiles) {
-            const int rem = prefix - (i - NBLK - nt_ext) * TN;
-            w0 = w1 = rem >= 32 ? 0xffffffffu : ((1u << rem) - 1u);
+    // mask words of my two rows for column tile i (fetched one tile ahead of their use)
+    auto mask_words = [&](int i, uint32_t (&w0)[TP], uint32_t (&w1)[TP]) {
+#pragma unroll
+        for (int p = 0; p < TP; ++p) {
+            w0[p] = w1[p] = 0u;
+            if (i < NBLK) {
+                const int wi = i * TP + p;
+                if (ok0 && wi < BW) w0[p] = __ldg(g_bmask + r0 * BW + wi);
+                if (ok1 && wi < BW) w1[p] = __ldg(g_bmask + r1 * BW + wi);
+            } else if (i - NBLK < nt_ext) {
+                const int wi = (i - NBLK) * TP + p;
+                if (ok0 && wi < maw) w0[p] = __ldg(g_emask + r0 * maw + wi);
+                if (ok1 && wi < maw) w1[p] = __ldg(g_emask + r1 * maw + wi);
+            } else if (i < n_tiles) {
+                const int rem = prefix - (i - NBLK - nt_ext) * TN - p * 32;
+                w0[p] = w1[p] = rem >= 32 ? 0xffffffffu : (rem > 0 ? (1u << rem) - 1u : 0u);
+            }
         }
     };
-    uint32_t w0n, w1n;
+    uint32_t w0n[TP], w1n[TP];
     mask_words(0, w0n, w1n);
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < NBLK;
         const int e = i - NBLK;                           // gathered tile number
-        const uint32_t w0 = w0n, w1 = w1n;
+        uint32_t w0[TP], w1[TP];
+#pragma unroll
+        for (int p = 0; p < TP; ++p) { w0[p] = w0n[p]; w1[p] = w1n[p]; }
         mask_words(i + 1, w0n, w1n);
         uint32_t kbase, vbase;
         if (blk) {
-            kbase = s_base + SM::KB + i * SM::TILE;
-            vbase = s_base + SM::VB + i * SM::TILE;
+            kbase = s_base + SM::KB + i * TP * SM::TILE;
+            vbase = s_base + SM::VB + i * TP * SM::TILE;
         } else {
             kbase = s_base + ((e & 1) ? SM::ST1 : SM::ST0);
-            vbase = kbase + SM::TILE;
+            vbase = kbase + TP * SM::TILE;
             cp_async_wait<1>();
             __syncthreads();
         }
-        const uint32_t occ = __reduce_or_sync(0xffffffffu, w0 | w1);   // columns any of my 16 rows use
-        const bool lo = (occ & 0xffffu) != 0u, hi = (occ >> 16) != 0u;
-
-        uint32_t pf[2][4];
-        if (occ) {
-            float s[4][4];
+        // 16-column groups any of my warp's 16 rows use
+        bool act[NG];
+        bool any = false;
 #pragma unroll
-            for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int p = 0; p < TP; ++p) {
+            const uint32_t occ = __reduce_or_sync(0xffffffffu, w0[p] | w1[p]);
+            act[2 * p] = (occ & 0xffffu) != 0u;
+            act[2 * p + 1] = (occ >> 16) != 0u;
+            any = any || occ != 0u;
+        }
+
+        uint32_t pf[NG][4];
+        if (any) {
+            // ---- S = Q K^T on the occupied groups (k-steps outermost: independent accumulators)
+            float s[2 * NG][4];
+#pragma unroll
+            for (int n = 0; n < 2 * NG; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
             const int krow = ((lane >> 4) << 3) + (lane & 7), kch = (lane >> 3) & 1;
 #pragma unroll
-            for (int cg = 0; cg < 2; ++cg) {
-                if (cg == 0 ? lo : hi) {
+            for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-                    for (int ks = 0; ks < KS; ++ks) {
+                for (int cg = 0; cg < NG; ++cg) {
+                    if (act[cg]) {
                         uint32_t kb[4];
-                        ldmatrix_x4(kb, kbase + TL::off(cg * 16 + krow, ks * 2 + kch));
+                        ldmatrix_x4(kb, kbase + (cg >> 1) * SM::TILE + TL::off((cg & 1) * 16 + krow, ks * 2 + kch));
                         MT::mma(s[2 * cg], qf[ks], kb[0], kb[1]);
                         MT::mma(s[2 * cg + 1], qf[ks], kb[2], kb[3]);
                     }
                 }
             }
+            // ---- mask, running max (raw units), probabilities
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                if (n < 2 ? lo : hi) {
-                    const int c = n * 8 + 2 * t;
-                    s[n][0] = ((w0 >> c) & 1u) ? s[n][0] : -INFINITY;
-                    s[n][1] = ((w0 >> c) & 2u) ? s[n][1] : -INFINITY;
-                    s[n][2] = ((w1 >> c) & 1u) ? s[n][2] : -INFINITY;
-                    s[n][3] = ((w1 >> c) & 2u) ? s[n][3] : -INFINITY;
+            for (int n = 0; n < 2 * NG; ++n) {
+                if (act[n >> 1]) {
+                    const int c = (n & 3) * 8 + 2 * t;
+                    const uint32_t b0 = w0[n >> 2] >> c, b1 = w1[n >> 2] >> c;
+                    s[n][0] = (b0 & 1u) ? s[n][0] : -INFINITY;
+                    s[n][1] = (b0 & 2u) ? s[n][1] : -INFINITY;
+                    s[n][2] = (b1 & 1u) ? s[n][2] : -INFINITY;
+                    s[n][3] = (b1 & 2u) ? s[n][3] : -INFINITY;
                     mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
                     mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
                 }
@@ -301,8 +326,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             m0 = mn0; m1 = mn1;
             float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                if (n < 2 ? lo : hi) {
+            for (int n = 0; n < 2 * NG; ++n) {
+                if (act[n >> 1]) {
                     const float p0 = fast_exp2(fmaf(s[n][0], c2, -mu0)), p1 = fast_exp2(fmaf(s[n][1], c2, -mu0));
                     const float p2 = fast_exp2(fmaf(s[n][2], c2, -mu1)), p3 = fast_exp2(fmaf(s[n][3], c2, -mu1));
                     ps0 += p0 + p1;
@@ -324,15 +349,16 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 
         if (blk && i == 0) alive = mbar_wait(bar_v, 0, a.status, b) && alive;   // the block's V rows
 
-        if (occ) {
+        if (any) {
+            // ---- O += P V
             const int vrow = (((lane >> 3) & 1) << 3) + (lane & 7), vch = lane >> 4;
 #pragma unroll
-            for (int cg = 0; cg < 2; ++cg) {
-                if (cg == 0 ? lo : hi) {
+            for (int cg = 0; cg < NG; ++cg) {
+                if (act[cg]) {
 #pragma unroll
                     for (int dp = 0; dp < ND / 2; ++dp) {
                         uint32_t vb[4];
-                        ldmatrix_x4_trans(vb, vbase + TL::off(cg * 16 + vrow, dp * 2 + vch));
+                        ldmatrix_x4_trans(vb, vbase + (cg >> 1) * SM::TILE + TL::off((cg & 1) * 16 + vrow, dp * 2 + vch));
                         MT::mma(acc[2 * dp], pf[cg], vb[0], vb[1]);
                         MT::mma(acc[2 * dp + 1], pf[cg], vb[2], vb[3]);
                     }
@@ -413,12 +439,11 @@ inline bool make_map(CUtensorMap *map, const void *base, bool bf16, int D, int r
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, int D, int BM>
+template <typename T, int D, int BM, int TN>
 cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
-    using SM = TmaSmem<D, BM>;
+    using SM = TmaSmem<D, BM, TN>;
     constexpr size_t smem = SM::BYTES;
     constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
-    // a dimension of size 1 may carry any stride; TMA wants strides that grow with the dimension
     alignas(64) CUtensorMap tq, tk, tv;
     if (!make_map(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
         !make_map(&tk, a.k, bf16, D, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
@@ -426,22 +451,36 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
         return cudaErrorNotSupported;
     static bool configured = false;                       // one process drives one device
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM>,
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
     dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
-    attn_tma_kernel<T, D, BM><<<grid, block, smem, stream>>>(a, tq, tk, tv);
+    attn_tma_kernel<T, D, BM, TN><<<grid, block, smem, stream>>>(a, tq, tk, tv);
     return cudaGetLastError();
 }
 
+// tile_cols: 32, 64, or 0 = by grid size: 64-column tiles up to about eight CTAs per SM (measured:
+// 128 and 512 CTAs are faster with 64, 4096 CTAs equal, 8192 CTAs 20 % faster with 32)
 template <typename T, int D>
-cudaError_t launch_tma_d(const AttnArgs &a, cudaStream_t stream) {
-    switch (a.bm) {
-        case 32: return launch_tma_inst<T, D, 32>(a, stream);
-        case 64: return launch_tma_inst<T, D, 64>(a, stream);
-        case 128: return launch_tma_inst<T, D, 128>(a, stream);
+cudaError_t launch_tma_d(const AttnArgs &a, int tile_cols, cudaStream_t stream) {
+    if (tile_cols == 0) {
+        const long long ctas = (long long)a.nb * a.H * a.Z;
+        tile_cols = ctas <= 8 * 148 ? 64 : 32;
+    }
+    if (tile_cols == 64) {
+        switch (a.bm) {
+            case 32: return launch_tma_inst<T, D, 32, 64>(a, stream);
+            case 64: return launch_tma_inst<T, D, 64, 64>(a, stream);
+            case 128: return launch_tma_inst<T, D, 128, 64>(a, stream);
+        }
+    } else {
+        switch (a.bm) {
+            case 32: return launch_tma_inst<T, D, 32, 32>(a, stream);
+            case 64: return launch_tma_inst<T, D, 64, 32>(a, stream);
+            case 128: return launch_tma_inst<T, D, 128, 32>(a, stream);
+        }
     }
     return cudaErrorNotSupported;
 }

@@ -48,7 +48,10 @@ enum fst_kernel {
     FST_KERNEL_AUTO = 0,
     FST_KERNEL_SIMT = 1,           /* fp32 arithmetic, any dtype / head_dim in {16,32,64,128}   */
     FST_KERNEL_MMA = 2,            /* tensor-core kernel, cp.async gathers: fp16/bf16, D 64/128  */
-    FST_KERNEL_TMA = 3             /* same arithmetic, bulk-copy-engine transfers + mbarriers    */
+    FST_KERNEL_TMA = 3,            /* same arithmetic, TMA tile loads + mbarriers, swizzled smem; */
+                                   /* 32- or 64-column tiles chosen by grid size                 */
+    FST_KERNEL_TMA_T32 = 4,        /* ... forced 32-column tiles (three CTAs per SM)             */
+    FST_KERNEL_TMA_T64 = 5         /* ... forced 64-column tiles (fewest softmax rounds)         */
 };
 
 int fst_version(void);

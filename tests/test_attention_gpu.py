@@ -30,7 +30,7 @@ def fst(built_lib):
 def kernels_for(dtype, d, bm):
     ks = ["auto", "simt"]
     if dtype in (torch.float16, torch.bfloat16) and d in (64, 128) and bm in (16, 32, 64, 128):
-        ks += ["mma"] + (["tma"] if bm >= 32 else [])
+        ks += ["mma"] + (["tma_t32", "tma_t64"] if bm >= 32 else [])
     return ks
 
 
@@ -136,7 +136,7 @@ def test_full_size_equal_scores_property(fst, name):
     q = torch.randn((T, H, n, D), generator=g).half()
     k = torch.zeros_like(v)
     meta = fst.build_tree_metadata(w.trees if T > 1 else w.trees[0], w.block_m, w.max_ancestors)
-    for kern in ("mma", "tma"):
+    for kern in ("mma", "tma_t32", "tma_t64"):
         o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
         for t in range(0, T, 9):
             want = chain_mean_values(w.trees[t], v[t].double().numpy())
@@ -156,7 +156,7 @@ def test_full_size_kernels_agree(fst):
     q, k, v = (x.cuda() for x in make_qkv(1, w.heads, w.n_nodes, w.n_nodes, w.head_dim, torch.float16, 17))
     meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors)
     base = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel="simt")
-    for kern in ("mma", "tma"):
+    for kern in ("mma", "tma_t32", "tma_t64"):
         o = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel=kern)
         assert maxabs(o, base) <= TOL_F16, kern
 
