@@ -11,7 +11,8 @@
 //   * every tile lives in shared memory in the 128-byte-swizzled layout TMA writes (16-byte
 //     chunk c of row r sits at chunk c ^ (r & 7)), which makes ldmatrix conflict free without
 //     padding; the gathered ancestor rows are placed into the same layout by cp.async;
-//   * Q is read with ldmatrix; its buffer doubles as the second gathered stage.
+//   * Q is read with ldmatrix; its buffer doubles as the second gathered stage and, at the end,
+//     as the staging tile from which O leaves through a TMA store.
 //
 // Every mbarrier wait is bounded in time: when it runs out the kernel records FST_DEV_TIMEOUT in
 // the status record and carries on to its exit instead of spinning.
@@ -64,6 +65,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
 
+// one box from shared memory back to a rank-4 tensor; rows past the end of the tensor are dropped
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // A tile is 32 rows; with D = 128 it is two 4 KB halves (columns 0-63, 64-127), each 32 rows of
 // 128 bytes in the swizzled layout.
 template <int D>
@@ -98,7 +105,8 @@ struct TmaSmem {
 template <typename T, int D, int BM, int TN>
 __global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : 1))
 attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
-                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const __grid_constant__ CUtensorMap tm_o) {
     using MT = MmaTraits<T>;
     using SM = TmaSmem<D, BM, TN>;
     using TL = SwzTile<D>;
@@ -134,8 +142,6 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 
     const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
     const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + h * a.vs_h;
-    T *op = static_cast<T *>(a.o) + z * a.os_z + h * a.os_h;
-
     const int lr = tid / CH, lc = tid % CH;               // my row-in-pass and 16-byte chunk
     const int r0 = warp * 16 + g, r1 = r0 + 8;            // my two rows inside the block
     const bool ok0 = row0 + r0 < n_q, ok1 = row0 + r1 < n_q;
@@ -381,27 +387,41 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         }
     }
 
-    // ---- epilogue: normalise and store each quad's 16-byte pieces directly
+    // ---- epilogue: normalise, stage O in the Q tiles (same swizzled layout; each warp writes its
+    //      own 16 rows, bank-conflict free), then one thread hands the tiles to TMA
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = (l0 > 0.f && alive) ? 1.f / l0 : 0.f, inv1 = (l1 > 0.f && alive) ? 1.f / l1 : 0.f;
-    if (ok0) {
-        uint32_t *o0 = reinterpret_cast<uint32_t *>(op + (long long)(row0 + r0) * a.os_n) + t;
+    if (nt_gat > 1) __syncthreads();                      // stage 1 shares this memory
+    {
+        const uint32_t ob0 = s_base + SM::QO + (r0 >> 5) * SM::TILE + t * 4;
+        const uint32_t ob1 = s_base + SM::QO + (r1 >> 5) * SM::TILE + t * 4;
 #pragma unroll
-        for (int d = 0; d < ND; ++d) o0[d * 4] = MT::pack(acc[d][0] * inv0, acc[d][1] * inv0);
+        for (int d = 0; d < ND; ++d) {
+            const uint32_t v0 = MT::pack(acc[d][0] * inv0, acc[d][1] * inv0);
+            const uint32_t v1 = MT::pack(acc[d][2] * inv1, acc[d][3] * inv1);
+            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ob0 + TL::off(r0 & 31, d)), "r"(v0) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ob1 + TL::off(r1 & 31, d)), "r"(v1) : "memory");
+        }
     }
-    if (ok1) {
-        uint32_t *o1 = reinterpret_cast<uint32_t *>(op + (long long)(row0 + r1) * a.os_n) + t;
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
 #pragma unroll
-        for (int d = 0; d < ND; ++d) o1[d * 4] = MT::pack(acc[d][2] * inv1, acc[d][3] * inv1);
+        for (int j = 0; j < NB32; ++j)
+#pragma unroll
+            for (int hf = 0; hf < TL::HALVES; ++hf)
+                tma_store_4d(&tm_o, s_base + SM::QO + j * SM::TILE + hf * 4096, hf * 64, row0 + j * 32, h, z);
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
     }
     if (a.lse != nullptr && t == 0) {
         float *lse = a.lse + (size_t(z) * a.H + h) * n_q;
         if (ok0) lse[row0 + r0] = m0 * c2 + log2f(l0);
         if (ok1) lse[row0 + r1] = m1 * c2 + log2f(l1);
     }
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // smem stays valid until read
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -444,10 +464,11 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
     using SM = TmaSmem<D, BM, TN>;
     constexpr size_t smem = SM::BYTES;
     constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
-    alignas(64) CUtensorMap tq, tk, tv;
+    alignas(64) CUtensorMap tq, tk, tv, to;
     if (!make_map(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
         !make_map(&tk, a.k, bf16, D, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z))
+        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
+        !make_map(&to, a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z))
         return cudaErrorNotSupported;
     static bool configured = false;                       // one process drives one device
     if (!configured) {
@@ -457,7 +478,7 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
-    attn_tma_kernel<T, D, BM, TN><<<grid, block, smem, stream>>>(a, tq, tk, tv);
+    attn_tma_kernel<T, D, BM, TN><<<grid, block, smem, stream>>>(a, tq, tk, tv, to);
     return cudaGetLastError();
 }
 
