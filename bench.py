@@ -37,6 +37,10 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the ncu captures summarised
+# in profiles/attn_tma_kernel_medusa256_forest64.md (same per-launch work as the bench)
+NCU_TRAFFIC_BYTES = {"medusa256": 6.36e6, "forest64": 515.7e6}
+
 METRIC = "tree_attn_gathered_kv_bandwidth"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
@@ -364,7 +368,7 @@ def run_ours(args, rank, world):
         "gpu_launches": args.steps * (L + 1),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name), "peak_source": f"of {peak_kind}",
                      "kernel": "attn_tma_kernel" if args.kernel in ("auto", "tma") else f"attn_{args.kernel}_kernel", "achieved_incl_q_o": (kv + info["q_o_bytes_per_call"]) / (launch_us * 1e-6) / 1e9,
                      "frac_of_nominal_8000": achieved / 8000.0},
     }
