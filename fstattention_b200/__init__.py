@@ -1,11 +1,14 @@
 """B200-native fused sparse tree attention: GPU tree precompute + tree attention kernels.
 
 Public surface (mirrors the reference's utils.py / fstattention.py):
-  create_fst_attention_kernel_inputs, build_tree_metadata, TreeMetadata, fst_attention
+  create_tree, create_full_attention_mask, create_fst_attention_kernel_inputs, DEPTH_MAPPING,
+  MAX_ANCESTOR_MAPPING, fst_attention; plus build_tree_metadata / TreeMetadata for parent arrays
 """
-from .utils import (TreeMetadata, build_tree_metadata, create_fst_attention_kernel_inputs,  # noqa: F401
+from .utils import (DEPTH_MAPPING, MAX_ANCESTOR_MAPPING, TreeMetadata, build_tree_metadata,  # noqa: F401
+                    create_fst_attention_kernel_inputs, create_full_attention_mask, create_tree,
                     lineage_from_parent, parent_from_lineage)
 from .fstattention import fst_attention, last_status  # noqa: F401
 
-__all__ = ["TreeMetadata", "build_tree_metadata", "create_fst_attention_kernel_inputs",
+__all__ = ["DEPTH_MAPPING", "MAX_ANCESTOR_MAPPING", "create_tree", "create_full_attention_mask",
+           "TreeMetadata", "build_tree_metadata", "create_fst_attention_kernel_inputs",
            "lineage_from_parent", "parent_from_lineage", "fst_attention", "last_status"]

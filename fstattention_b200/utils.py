@@ -18,6 +18,11 @@ from . import _lib
 
 TreeLike = Union[torch.Tensor, Sequence[int], Sequence[Sequence[int]]]
 
+# Same tables as the reference's utils.py:4-24: tree depth that fills a context of 2^k - 4 nodes,
+# and the ancestor bound its benchmark uses for it.
+DEPTH_MAPPING = {2 ** (10 + i): 7 + i for i in range(8)}
+MAX_ANCESTOR_MAPPING = {2 ** (10 + i): 64 for i in range(8)}
+
 
 class TreeMetadata:
     """Block metadata of one tree or a batch of trees, resident on one GPU.
@@ -196,3 +201,56 @@ def lineage_from_parent(parent: Sequence[int]):
             lin[i, : level[p]] = lin[p, : level[p]]
             lin[i, level[p]] = p
     return lin, torch.tensor(level, dtype=torch.long)
+
+
+def create_tree(depth: int = 7, topk: int = 4, left_weight_factor: float = 0.5):
+    """The reference's synthetic left-weighted forest (utils.py:27-77), built without loops over
+    nodes.
+
+    ``topk`` roots; level sizes follow ``size[l] = topk * int(size[l-1] * left_weight_factor)``
+    and node ``r`` of a level hangs under node ``r // topk`` of the level above.  With the
+    defaults the forest has 2^(depth+3) - 4 nodes.  Returns ``lineage [N, depth + 1]`` (ancestor
+    of each node per level, -1 padded, the node itself not included) and ``level_lookup [N]``,
+    both int64 on the CPU, equal to what the reference returns.
+    """
+    sizes = [topk]
+    for _ in range(depth):
+        sizes.append(topk * int(sizes[-1] * left_weight_factor))
+    starts = [0]
+    for sz in sizes:
+        starts.append(starts[-1] + sz)
+    n = starts[-1]
+    level = torch.repeat_interleave(torch.arange(len(sizes)), torch.tensor(sizes))
+    start_of = torch.tensor(starts[:-1])[level]
+    rel = torch.arange(n) - start_of
+    parent = torch.where(level > 0, torch.tensor([0] + starts[:-2])[level] + rel // topk,
+                         torch.full((n,), -1, dtype=torch.long))
+    lineage = torch.full((n, depth + 1), -1, dtype=torch.long)
+    anc = parent.clone()
+    for step in range(1, depth + 1):                     # ancestor `step` levels up, all nodes at once
+        has = anc >= 0
+        rows = torch.nonzero(has).squeeze(1)
+        lineage[rows, level[rows] - step] = anc[rows]
+        anc = torch.where(has, parent[anc.clamp_min(0)], anc)
+    return lineage, level.long()
+
+
+def create_full_attention_mask(lineage: torch.Tensor) -> torch.Tensor:
+    """Dense mask "node attends to itself and its ancestors", as the reference builds it
+    (utils.py:79-102), on the device ``lineage`` lives on.
+
+    float32 ``[N + 4, N + 4]``: the reference always appends four zero rows and columns (its
+    trees have 2^k - 4 nodes), clears the last column while removing the -1 pads and restores
+    only the last node's self entry.  For other sizes pad ``mask[:N, :N]`` yourself.
+    """
+    n = lineage.shape[0]
+    dev = lineage.device
+    mask = torch.zeros((n, n), dtype=torch.bool, device=dev)
+    rows = torch.arange(n, device=dev).unsqueeze(1).expand_as(lineage)
+    mask[rows.reshape(-1), lineage.reshape(-1)] = True    # -1 lands in the last column
+    mask[torch.arange(n, device=dev), torch.arange(n, device=dev)] = True
+    mask[:, -1] = False
+    mask[-1, -1] = True
+    out = torch.zeros((n + 4, n + 4), dtype=torch.float32, device=dev)
+    out[:n, :n] = mask
+    return out

@@ -234,3 +234,39 @@ def test_argument_errors_are_python_errors(fst):
         fst.fst_attention(odd, odd, odd, meta, sm_scale=1.0, kernel="mma")
     fst.fst_attention(odd, odd, odd, meta, sm_scale=1.0, kernel="simt")   # the SIMT kernel takes it
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shared_kv_prefix", [True, False])
+def test_reference_test_op_recipe(fst, shared_kv_prefix):
+    """The reference's own test, step for step (fstattention.py:183-228), with this package
+    behind the reference's names: Z=2, H=2, N_CTX=2048, D=64, fp16, seed 20, std 0.5, scale 0.5,
+    BLOCK_M=128, MAX_ANCESTORS=64, atol 1e-2 on all rows but the four pad rows."""
+    Z, H, N_CTX, D_HEAD, dtype = 2, 2, 2 ** 11, 64, torch.float16
+    torch.manual_seed(20)
+    q = torch.empty((Z, H, N_CTX, D_HEAD), dtype=dtype, device="cuda").normal_(mean=0.0, std=0.5)
+    kv_rows = 2 * N_CTX if shared_kv_prefix else N_CTX
+    k = torch.empty((Z, H, kv_rows, D_HEAD), dtype=dtype, device="cuda").normal_(mean=0.0, std=0.5)
+    v = torch.empty((Z, H, kv_rows, D_HEAD), dtype=dtype, device="cuda").normal_(mean=0.0, std=0.5)
+    sm_scale = 0.5
+
+    lineage, level_lookup = fst.create_tree(depth=fst.DEPTH_MAPPING[N_CTX])
+    full_mask = fst.create_full_attention_mask(lineage)
+    BLOCK_M = 128
+    MAX_ANCESTORS = fst.MAX_ANCESTOR_MAPPING[N_CTX]
+    ancestor_idx, ancestor_mask, leaf_idx = fst.create_fst_attention_kernel_inputs(
+        lineage, level_lookup, block_m=BLOCK_M, max_ancestors=MAX_ANCESTORS)
+    if shared_kv_prefix:
+        full_mask = torch.cat((torch.ones((N_CTX, N_CTX), dtype=torch.bool), full_mask), dim=1)
+        ancestor_idx += N_CTX
+        leaf_idx += N_CTX
+
+    M = full_mask.to("cuda")
+    p = torch.matmul(q, k.transpose(2, 3)) * sm_scale
+    p[:, :, M == 0] = float("-inf")
+    p = torch.softmax(p.float(), dim=-1).half()
+    ref_out = torch.matmul(p, v)
+
+    ancestor_idx, ancestor_mask, leaf_idx = ancestor_idx.to("cuda"), ancestor_mask.to("cuda"), leaf_idx.to("cuda")
+    out = fst.fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale).half()
+    assert torch.allclose(ref_out[:, :, :-4], out[:, :, :-4], atol=1e-2, rtol=0)
+    assert fst.last_status() == 0

@@ -83,3 +83,29 @@ def test_workload_definitions():
     deep = configs.workload("deep4096").trees[0]
     assert len(deep) == 4096 and all(p < i for i, p in enumerate(deep))
     assert len(configs.deep_chain_tree(0, 4096, chains=64)) == 2579
+
+
+def test_create_tree_and_full_mask_match_reference(metadata_golden):
+    """Fixture generator and dense mask builder against what the reference produced."""
+    import fstattention_b200 as fst
+    from oracle import tree_oracle as orc
+    for depth, key in ((3, "reftree_d3_bm32"), (7, "reftree_d7_bm128")):
+        case = metadata_golden[key]
+        lin, lvl = fst.create_tree(depth=depth)
+        ref_lin, ref_lvl = orc.lineage_from_parent(case["parent"].tolist())
+        assert lin.dtype == torch.long and lvl.dtype == torch.long
+        assert lin.shape == (2 ** (depth + 3) - 4, depth + 1)
+        assert torch.equal(lin, ref_lin) and torch.equal(lvl, ref_lvl)
+    assert fst.DEPTH_MAPPING[2 ** 11] == 8 and fst.MAX_ANCESTOR_MAPPING[2 ** 16] == 64
+    seen = 0
+    for name, case in metadata_golden.items():
+        if "full_mask_bits" not in case:
+            continue
+        shape = tuple(case["full_mask_shape"])
+        ref = np.unpackbits(case["full_mask_bits"], axis=1)[:, : shape[1]].astype(np.float32)
+        lin, _ = orc.lineage_from_parent(case["parent"].tolist())
+        got = fst.create_full_attention_mask(lin)
+        assert got.dtype == torch.float32 and tuple(got.shape) == shape
+        assert np.array_equal(got.numpy(), ref), name
+        seen += 1
+    assert seen >= 5
