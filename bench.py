@@ -82,6 +82,7 @@ def describe(w, layers):
     rows = 0
     for par in w.trees:
         rows += gathered_rows_of(par, w.block_m)
+        rows += w.prefix * -(-len(par) // w.block_m)       # every block reads the whole prefix
     kv_bytes = rows * w.heads * w.head_dim * es * 2
     qo_bytes = 2 * len(w.trees) * w.heads * w.n_nodes * w.head_dim * es
     return {"gathered_kv_bytes_per_call": kv_bytes, "q_o_bytes_per_call": qo_bytes,
@@ -212,8 +213,8 @@ def run_ours(args, rank, world):
     T, H, N, D, L = len(w.trees), w.heads, w.n_nodes, w.head_dim, args.layers
 
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    layers = [tuple(torch.randn((T, H, N, D), generator=g, device=dev, dtype=torch.float32).to(dtype)
-                    for _ in range(3)) for _ in range(L)]
+    layers = [tuple(torch.randn((T, H, N + (w.prefix if i else 0), D), generator=g, device=dev,
+                                dtype=torch.float32).to(dtype) for i in range(3)) for _ in range(L)]
     outs = [torch.empty((T, H, N, D), device=dev, dtype=dtype) for _ in range(L)]
     parent = torch.tensor(w.trees if T > 1 else w.trees[0], dtype=torch.int32, device=dev)
     meta = fst.build_tree_metadata(parent, w.block_m, w.max_ancestors, reference_format=False)
@@ -310,7 +311,7 @@ def run_ours(args, rank, world):
         host_in = [tuple(t.cpu().pin_memory() for t in trip) for trip in layers[:e2e_layers]]
         host_out = [torch.empty((T, H, N, D), dtype=dtype).pin_memory() for _ in range(e2e_layers)]
         host_parent = parent.cpu().pin_memory()
-        dq, dk, dv = (torch.empty_like(t) for t in layers[0])
+        dq, dk, dv = (torch.empty_like(t) for t in layers[0])    # k, v carry the prefix rows
         dpar = torch.empty_like(parent)
 
         def e2e_step():
@@ -338,8 +339,9 @@ def run_ours(args, rank, world):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = t.item()
         tensor_bytes = T * H * N * D * (4 if w.dtype == "fp32" else 2)
+        in_bytes = sum(t.numel() * t.element_size() for t in layers[0])
         e2e = {"value": world * kv * e2e_layers / dt / 1e9, "unit": UNIT,
-               "h2d_bytes_per_step": e2e_layers * 3 * tensor_bytes + parent.numel() * 4,
+               "h2d_bytes_per_step": e2e_layers * in_bytes + parent.numel() * 4,
                "d2h_bytes_per_step": e2e_layers * tensor_bytes,
                "ms_per_step": dt * 1e3, "calls_per_step": e2e_layers,
                "us_per_call": dt * 1e6 / e2e_layers}
@@ -355,7 +357,7 @@ def run_ours(args, rank, world):
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
         "config": {"workload": w.name, "trees": T, "nodes": N, "heads": H, "head_dim": D,
-                   "block_m": w.block_m, "max_ancestors": w.max_ancestors,
+                   "block_m": w.block_m, "max_ancestors": w.max_ancestors, "prefix": w.prefix,
                    "calls_per_step": L, "step": "1 precompute launch + calls_per_step attention launches (CUDA graph)",
                    "l2": f"{L} distinct layer buffers, {resident_mb:.0f} MB resident > 126 MB L2",
                    "kernel": args.kernel, "per_rank": "same step on every rank, own inputs"},

@@ -97,6 +97,7 @@ class Workload:
     block_m: int
     max_ancestors: int
     shard: str = "none"             # "none" | "tree" | "head"
+    prefix: int = 0                 # shared K/V rows every query attends to (the prompt)
     notes: str = ""
     extras: dict = field(default_factory=dict)
 
@@ -127,6 +128,10 @@ def workload(name: str, step: int = 0) -> Workload:
     if name == "deep4096":
         return Workload(name, [deep_chain_tree(0, 4096)], heads=64, head_dim=128, dtype="fp16",
                         block_m=64, max_ancestors=128, shard="head")
+    if name == "medusa256_prefix4096":
+        return Workload(name, [left_weighted_tree()], heads=32, head_dim=128, dtype="fp16",
+                        block_m=64, max_ancestors=64, prefix=4096,
+                        notes="decode step: 4096-token prompt shared by the 256-node tree")
     raise KeyError(name)
 
 
