@@ -19,7 +19,8 @@ DEV_MALFORMED_TREE, DEV_ANCESTOR_OVERFLOW, DEV_INDEX_RANGE = 16, 17, 18
 # every symbol include/fstattn_b200.h declares
 EXPORTS = ("fst_version", "fst_status_string", "fst_packed_meta_bytes", "fst_precompute",
            "fst_pack_metadata", "fst_attention_fwd", "fst_attention_ref_workspace_bytes",
-           "fst_attention_fwd_ref", "fst_attention_fwd_ref_static")
+           "fst_attention_fwd_ref", "fst_attention_fwd_ref_static",
+           "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv")
 STATIC_SCRATCH_BYTES = 512 * 1024
 
 _lib = None
@@ -42,6 +43,11 @@ def _declare(lib):
     lib.fst_attention_fwd.restype = _i
     lib.fst_attention_fwd.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i]
                                       + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _p])
+    lib.fst_attention_split_workspace_bytes.restype = _sz
+    lib.fst_attention_split_workspace_bytes.argtypes = [_i, _i, _i, _i, _i]
+    lib.fst_attention_fwd_splitkv.restype = _i
+    lib.fst_attention_fwd_splitkv.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i]
+                                              + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _i, _p, _sz, _p, _p])
     lib.fst_attention_ref_workspace_bytes.restype = _sz
     lib.fst_attention_ref_workspace_bytes.argtypes = [_i, _i, _i, _i]
     lib.fst_attention_fwd_ref.restype = _i

@@ -119,14 +119,19 @@ int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
                                    static_cast<cudaStream_t>(stream)));
 }
 
-int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse,
+size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, int kv_splits) {
+    if (Z <= 0 || H <= 0 || n_q <= 0 || head_dim <= 0 || kv_splits <= 1) return 0;
+    return size_t(kv_splits) * Z * H * n_q * (size_t(head_dim) + 1) * sizeof(float);
+}
+
+static int attention_fwd_impl(const void *q, const void *k, const void *v, void *o, float *lse,
                       const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
                       int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
                       int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
                       int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
                       int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
-                      int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
-                      void *stream) {
+                      int max_ancestors, float sm_scale, int dtype, int kernel, int kv_splits,
+                      void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
     if (!q || !k || !v || !o || !packed || Z <= 0 || H <= 0 || n_q <= 0 || n_kv < n_q ||
         block_m <= 0 || max_ancestors <= 0)
         return FST_ERR_INVALID_ARG;
@@ -148,6 +153,9 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
     a.bm = block_m; a.ma = max_ancestors; a.nb = (n_q + block_m - 1) / block_m;
     a.scale_log2 = sm_scale * 1.4426950408889634f;
     a.status = status;
+    a.n_splits = 1;
+    a.part_o = nullptr;
+    a.part_lse = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // the tensor-core kernel moves 16-byte pieces: every row must start on a 16-byte boundary
@@ -168,10 +176,55 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
         return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
+    if (kv_splits > 1 && a.prefix > 0 && choice != FST_KERNEL_MMA) {
+        // the prefix is cut into kv_splits runs of tiles; partial results go through the workspace
+        const size_t need = fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits);
+        if (!workspace || workspace_bytes < need) return FST_ERR_WORKSPACE;
+        if (!aligned16(workspace)) return FST_ERR_ALIGNMENT;
+        a.n_splits = kv_splits;
+        a.part_o = static_cast<float *>(workspace);
+        a.part_lse = a.part_o + size_t(kv_splits) * Z * H * n_q * head_dim;
+    }
     cudaError_t e = launch_attention_mma(a, dtype, choice, st);
     // shapes or strides the TMA variant cannot describe fall back to the cp.async variant
-    if (e == cudaErrorNotSupported && automatic) e = launch_attention_mma(a, dtype, FST_KERNEL_MMA, st);
+    if (e == cudaErrorNotSupported && automatic) {
+        a.n_splits = 1;
+        e = launch_attention_mma(a, dtype, FST_KERNEL_MMA, st);
+    }
     return cuda_status(e);
+}
+
+int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse,
+                      const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
+                      int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                      int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                      int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                      int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
+                      int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
+                      void *stream) {
+    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, n_q, n_kv, head_dim,
+                              q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                              v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
+                              block_m, max_ancestors, sm_scale, dtype, kernel, 1, nullptr, 0, status,
+                              stream);
+}
+
+int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void *o, float *lse,
+                              const void *packed, size_t meta_tree_stride, int Z, int H, int n_q,
+                              int n_kv, int head_dim, int64_t q_stride_z, int64_t q_stride_h,
+                              int64_t q_stride_n, int64_t k_stride_z, int64_t k_stride_h,
+                              int64_t k_stride_n, int64_t v_stride_z, int64_t v_stride_h,
+                              int64_t v_stride_n, int64_t o_stride_z, int64_t o_stride_h,
+                              int64_t o_stride_n, int block_m, int max_ancestors, float sm_scale,
+                              int dtype, int kernel, int kv_splits, void *workspace,
+                              size_t workspace_bytes, int32_t *status, void *stream) {
+    if (kv_splits < 1) return FST_ERR_INVALID_ARG;
+    if (kv_splits > 1 && (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
+    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, n_q, n_kv, head_dim,
+                              q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                              v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
+                              block_m, max_ancestors, sm_scale, dtype, kernel, kv_splits, workspace,
+                              workspace_bytes, status, stream);
 }
 
 size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m, int max_ancestors) {

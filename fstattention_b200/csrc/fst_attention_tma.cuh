@@ -125,12 +125,20 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;    // swizzle atoms are 1 KB
-    const int b = blockIdx.x, h = blockIdx.y, z = blockIdx.z;
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int z = blockIdx.z / a.n_splits, split = blockIdx.z - z * a.n_splits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = b * BM;
     const int prefix = a.prefix, n_q = a.n_q;
     const uint32_t bar_qk = s_base + SM::BAR, bar_v = bar_qk + 8;
+    // With the prefix split over several CTAs, split 0 also owns the tree part (block rows and
+    // external ancestors); every split takes a contiguous run of prefix tiles.
+    const bool tree = split == 0;
+    const int pt_total = (prefix + TN - 1) / TN, pt_per = (pt_total + a.n_splits - 1) / a.n_splits;
+    const int pt_lo = min(split * pt_per, pt_total), pt_hi = min(pt_lo + pt_per, pt_total);
+    const int p_lo = pt_lo * TN, p_end = min(prefix, pt_hi * TN);      // my prefix rows [p_lo, p_end)
+    const int nblk = tree ? SM::NBT : 0;
 
     const PackedLayout L = packed_layout(a.nb, BM, a.ma);
     const int maw = L.maw;
@@ -138,7 +146,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     const int32_t *g_idx = reinterpret_cast<const int32_t *>(blob + L.off_idx) + size_t(b) * a.ma;
     const uint32_t *g_emask = reinterpret_cast<const uint32_t *>(blob + L.off_emask) + size_t(b) * BM * maw;
     const uint32_t *g_bmask = reinterpret_cast<const uint32_t *>(blob + L.off_bmask) + size_t(b) * BM * BW;
-    const int count = __ldg(reinterpret_cast<const int32_t *>(blob + L.off_count) + b);
+    const int count = tree ? __ldg(reinterpret_cast<const int32_t *>(blob + L.off_count) + b) : 0;
 
     const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
     const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + h * a.vs_h;
@@ -162,20 +170,23 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         mbar_init(bar_qk, 1);
         mbar_init(bar_v, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        mbar_arrive_expect_tx(bar_qk, 2 * NB32 * SM::TILE);
+        mbar_arrive_expect_tx(bar_qk, (tree ? 2 : 1) * NB32 * SM::TILE);
 #pragma unroll
         for (int j = 0; j < NB32; ++j)
 #pragma unroll
             for (int hf = 0; hf < TL::HALVES; ++hf) {
-                tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, h, z, bar_qk);
+                if (tree)
+                    tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, h, z, bar_qk);
                 tma_load_4d(s_base + SM::QO + j * SM::TILE + hf * 4096, &tm_q, hf * 64, row0 + j * 32, h, z, bar_qk);
             }
-        mbar_arrive_expect_tx(bar_v, NB32 * SM::TILE);
+        if (tree) {
+            mbar_arrive_expect_tx(bar_v, NB32 * SM::TILE);
 #pragma unroll
-        for (int j = 0; j < NB32; ++j)
+            for (int j = 0; j < NB32; ++j)
 #pragma unroll
-            for (int hf = 0; hf < TL::HALVES; ++hf)
-                tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, h, z, bar_v);
+                for (int hf = 0; hf < TL::HALVES; ++hf)
+                    tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, h, z, bar_v);
+        }
     }
 
     // ---- gathered tiles (cp.async into the swizzled layout): external ancestors, then prefix
@@ -192,8 +203,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 if (node[j] >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, e * TN + s);
                 if (ok) rr = prefix + node[j];
             } else {
-                const int p = (e - nt_ext_of<TN>(count, a.ma)) * TN + s;
-                ok = p < prefix;
+                const int p = p_lo + (e - nt_ext_of<TN>(count, a.ma)) * TN + s;
+                ok = p < p_end;
                 if (ok) rr = p;
             }
             const uint32_t o = (s >> 5) * SM::TILE + TL::off(s & 31, lc);
@@ -207,7 +218,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         cp_async_commit();                                // group 0
     }
     const int nt_ext = nt_ext_of<TN>(count, a.ma);
-    const int nt_gat = nt_ext + (prefix + TN - 1) / TN;
+    const int nt_gat = nt_ext + (pt_hi - pt_lo);
     if (prefix != 0) {
         if (nt_gat > 0) load_gathered(0, 0, nt_ext > 0, nodeA);
         cp_async_commit();                                // group 0
@@ -237,22 +248,22 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // m in raw score units; l is my share
     const float c2 = a.scale_log2;
 
-    const int n_tiles = NBLK + nt_gat;
+    const int n_tiles = nblk + nt_gat;
     // mask words of my two rows for column tile i (fetched one tile ahead of their use)
     auto mask_words = [&](int i, uint32_t (&w0)[TP], uint32_t (&w1)[TP]) {
 #pragma unroll
         for (int p = 0; p < TP; ++p) {
             w0[p] = w1[p] = 0u;
-            if (i < NBLK) {
+            if (i < nblk) {
                 const int wi = i * TP + p;
                 if (ok0 && wi < BW) w0[p] = __ldg(g_bmask + r0 * BW + wi);
                 if (ok1 && wi < BW) w1[p] = __ldg(g_bmask + r1 * BW + wi);
-            } else if (i - NBLK < nt_ext) {
-                const int wi = (i - NBLK) * TP + p;
+            } else if (i - nblk < nt_ext) {
+                const int wi = (i - nblk) * TP + p;
                 if (ok0 && wi < maw) w0[p] = __ldg(g_emask + r0 * maw + wi);
                 if (ok1 && wi < maw) w1[p] = __ldg(g_emask + r1 * maw + wi);
             } else if (i < n_tiles) {
-                const int rem = prefix - (i - NBLK - nt_ext) * TN - p * 32;
+                const int rem = p_end - p_lo - (i - nblk - nt_ext) * TN - p * 32;
                 w0[p] = w1[p] = rem >= 32 ? 0xffffffffu : (rem > 0 ? (1u << rem) - 1u : 0u);
             }
         }
@@ -261,8 +272,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     mask_words(0, w0n, w1n);
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
-        const bool blk = i < NBLK;
-        const int e = i - NBLK;                           // gathered tile number
+        const bool blk = i < nblk;
+        const int e = i - nblk;                           // gathered tile number
         uint32_t w0[TP], w1[TP];
 #pragma unroll
         for (int p = 0; p < TP; ++p) { w0[p] = w0n[p]; w1[p] = w1n[p]; }
@@ -394,6 +405,24 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = (l0 > 0.f && alive) ? 1.f / l0 : 0.f, inv1 = (l1 > 0.f && alive) ? 1.f / l1 : 0.f;
+    if (a.n_splits > 1) {
+        // partial result of this split: normalised rows in fp32 plus their log-sum-exp; the
+        // combine kernel weighs the splits against each other
+        const size_t prow = ((size_t(split) * a.Z + z) * a.H + h) * n_q + row0;
+        if (ok0) {
+            float2 *o0 = reinterpret_cast<float2 *>(a.part_o + (prow + r0) * D) + t;
+#pragma unroll
+            for (int d = 0; d < ND; ++d) o0[d * 4] = make_float2(acc[d][0] * inv0, acc[d][1] * inv0);
+            if (t == 0) a.part_lse[prow + r0] = l0 > 0.f ? m0 * c2 + log2f(l0) : -INFINITY;
+        }
+        if (ok1) {
+            float2 *o1 = reinterpret_cast<float2 *>(a.part_o + (prow + r1) * D) + t;
+#pragma unroll
+            for (int d = 0; d < ND; ++d) o1[d * 4] = make_float2(acc[d][2] * inv1, acc[d][3] * inv1);
+            if (t == 0) a.part_lse[prow + r1] = l1 > 0.f ? m1 * c2 + log2f(l1) : -INFINITY;
+        }
+        return;
+    }
     if (nt_gat > 1) __syncthreads();                      // stage 1 shares this memory
     {
         const uint32_t ob0 = s_base + SM::QO + (r0 >> 5) * SM::TILE + t * 4;
@@ -422,6 +451,41 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         if (ok1) lse[row0 + r1] = m1 * c2 + log2f(l1);
     }
     if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // smem stays valid until read
+}
+
+// Merge the partial results of a split prefix: O = sum_s 2^(L_s - L) O_s with L the log-sum-exp of
+// the L_s.  One thread per (row, four output columns).
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+combine_splits_kernel(const AttnArgs a) {
+    constexpr int CPR = D / 4;                            // threads per row
+    const size_t rows = size_t(a.Z) * a.H * a.n_q;
+    const size_t idx = size_t(blockIdx.x) * 128 + threadIdx.x;
+    const size_t row = idx / CPR;
+    const int c = int(idx - row * CPR) * 4;
+    if (row >= rows) return;
+    float big = -INFINITY;
+    for (int s = 0; s < a.n_splits; ++s) big = fmaxf(big, a.part_lse[size_t(s) * rows + row]);
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    float wsum = 0.f;
+    for (int s = 0; s < a.n_splits; ++s) {
+        const float ls = a.part_lse[size_t(s) * rows + row];
+        if (ls == -INFINITY) continue;
+        const float w = exp2f(ls - big);
+        const float4 v = *reinterpret_cast<const float4 *>(a.part_o + (size_t(s) * rows + row) * D + c);
+        sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y);
+        sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+        wsum += w;
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    const size_t n = row % a.n_q, zh = row / a.n_q;
+    const size_t hh = zh % a.H, zz = zh / a.H;
+    T *op = static_cast<T *>(a.o) + zz * a.os_z + hh * a.os_h + n * a.os_n + c;
+    uint2 packed;
+    packed.x = MmaTraits<T>::pack(sum.x * inv, sum.y * inv);
+    packed.y = MmaTraits<T>::pack(sum.z * inv, sum.w * inv);
+    *reinterpret_cast<uint2 *>(op) = packed;
+    if (a.lse != nullptr && c == 0) a.lse[row] = big + log2f(wsum);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -477,8 +541,13 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
+    if (a.n_splits < 1 || (long long)a.Z * a.n_splits > 65535) return cudaErrorInvalidValue;
+    dim3 grid(a.nb, a.H, a.Z * a.n_splits), block(BM * 2);
     attn_tma_kernel<T, D, BM, TN><<<grid, block, smem, stream>>>(a, tq, tk, tv, to);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || a.n_splits == 1) return e;
+    const size_t items = size_t(a.Z) * a.H * a.n_q * (D / 4);
+    combine_splits_kernel<T, D><<<unsigned((items + 127) / 128), 128, 0, stream>>>(a);
     return cudaGetLastError();
 }
 
@@ -487,7 +556,7 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
 template <typename T, int D>
 cudaError_t launch_tma_d(const AttnArgs &a, int tile_cols, cudaStream_t stream) {
     if (tile_cols == 0) {
-        const long long ctas = (long long)a.nb * a.H * a.Z;
+        const long long ctas = (long long)a.nb * a.H * a.Z * a.n_splits;
         tile_cols = ctas <= 8 * 148 ? 64 : 32;
     }
     if (tile_cols == 64) {

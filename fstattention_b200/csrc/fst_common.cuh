@@ -66,6 +66,11 @@ struct AttnArgs {
     int bm, ma, nb;
     float scale_log2;      // sm_scale * log2(e)
     int32_t *status;
+    // split of the shared prefix over n_splits CTAs per (block, head, batch): partial outputs
+    // [n_splits][Z][H][n_q][D] (float, normalised) and their base-2 log-sum-exps; 1 = no split
+    int n_splits;
+    float *part_o;
+    float *part_lse;
 };
 
 cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);

@@ -42,9 +42,30 @@ def _strides(t):
     return [t.stride(0), t.stride(1), t.stride(2)]
 
 
+_SMS = {}
+
+
+def _pick_splits(kv_splits, q, prefix, block_m, kernel) -> int:
+    """How many CTAs share one (block, head, batch)'s prefix.  Only the tensor-core kernels
+    split; the automatic choice aims at about four CTAs per SM and at least eight 64-row
+    tiles per split."""
+    if q.dtype not in (torch.float16, torch.bfloat16) or q.shape[-1] not in (64, 128) \
+            or block_m not in (32, 64, 128) or kernel in ("simt", "mma") or prefix <= 0:
+        return 1
+    if kv_splits is not None:
+        return max(1, int(kv_splits))
+    dev = q.device
+    sms = _SMS.get(dev)
+    if sms is None:
+        sms = _SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    ctas = q.shape[0] * q.shape[1] * -(-q.shape[2] // block_m)
+    want = max(1, (4 * sms) // max(ctas, 1))
+    return int(max(1, min(want, prefix // 512, 65535 // max(q.shape[0], 1))))
+
+
 def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_scale=None,
                   BLOCK_M=128, MAX_ANCESTORS=64, *, out: Optional[torch.Tensor] = None,
-                  return_lse: bool = False, kernel: str = "auto"):
+                  return_lse: bool = False, kernel: str = "auto", kv_splits: Optional[int] = None):
     """Fused sparse tree attention forward.
 
     ``ancestor_idx, ancestor_mask, leaf_idx`` are the tensors returned by
@@ -54,6 +75,10 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     Alternatively pass a ``TreeMetadata`` as ``ancestor_idx`` and leave the other two ``None``;
     its block size and ancestor bound are used.  Metadata with a leading tree dimension of size
     ``Z`` gives every batch element its own tree.
+
+    ``kv_splits`` cuts a shared prefix into that many runs handled by separate CTAs and merged
+    afterwards (packed metadata only); ``None`` picks a split that fills the GPU when the tree
+    alone does not.
 
     Asserts like the reference (fstattention.py:155-157): equal head dims, in {16, 32, 64, 128}.
     """
@@ -94,11 +119,17 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 raise ValueError("BLOCK_M / MAX_ANCESTORS differ from the ones the metadata was built with")
             if meta.n_blocks != -(-n_q // BLOCK_M):
                 raise ValueError("metadata block count does not match q")
-            rc = lib.fst_attention_fwd(
+            splits = _pick_splits(kv_splits, q, n_kv - n_q, BLOCK_M, kernel)
+            ws, ws_bytes = None, 0
+            if splits > 1:
+                ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, splits))
+                ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            rc = lib.fst_attention_fwd_splitkv(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                 lse.data_ptr() if lse is not None else None,
                 meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0,
                 *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern,
+                splits, ws.data_ptr() if ws is not None else None, ws_bytes,
                 status.data_ptr(), stream)
             _lib.check(rc, "fst_attention_fwd")
         else:

@@ -137,6 +137,26 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
                       int32_t *status, void *stream);
 
 /*
+ * fst_attention_fwd with the shared prefix cut into kv_splits runs of rows, each handled by its
+ * own CTA per (block, head, batch) - the decode case, where a long prompt meets a tree too small
+ * to fill the GPU (the reference walks the prefix in one program, fstattention.py:113-136).
+ * Partial results (fp32) and their log-sum-exps pass through `workspace`
+ * (fst_attention_split_workspace_bytes bytes, 16-byte aligned, scratch) and a second kernel merges
+ * them.  kv_splits = 1, or no prefix, is fst_attention_fwd.  Tensor-core kernels only.
+ */
+size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, int kv_splits);
+int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void *o, float *lse,
+                              const void *packed, size_t meta_tree_stride,
+                              int Z, int H, int n_q, int n_kv, int head_dim,
+                              int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                              int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                              int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                              int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                              int block_m, int max_ancestors, float sm_scale, int dtype, int kernel,
+                              int kv_splits, void *workspace, size_t workspace_bytes,
+                              int32_t *status, void *stream);
+
+/*
  * The same with reference-format metadata, i.e. exactly the arguments of the reference's
  * fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale, BLOCK_M,
  * MAX_ANCESTORS) (fstattention.py:153).  Index tensors hold absolute K/V rows

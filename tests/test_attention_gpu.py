@@ -270,3 +270,26 @@ def test_reference_test_op_recipe(fst, shared_kv_prefix):
     out = fst.fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale).half()
     assert torch.allclose(ref_out[:, :, :-4], out[:, :, :-4], atol=1e-2, rtol=0)
     assert fst.last_status() == 0
+
+
+@pytest.mark.parametrize("prefix,splits", [(1000, 3), (4096, 8), (130, 2), (64, 5)])
+def test_prefix_split_over_ctas(fst, prefix, splits):
+    """A shared prefix cut into runs handled by separate CTAs and merged afterwards gives the
+    same output and log-sum-exp as the single-pass kernel and as the oracle."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D = 256, 3, 128
+    q, k, v = make_qkv(2, H, n, prefix + n, D, torch.float16, seed=21)
+    meta = fst.build_tree_metadata(par, 64, 64)
+    scale = D ** -0.5
+    exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
+    one, lse_one = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kv_splits=1, return_lse=True)
+    for kern in ("tma_t32", "tma_t64", "auto"):
+        out, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kv_splits=splits,
+                                     return_lse=True, kernel=kern)
+        assert maxabs(out.cpu(), exact) <= TOL_F16, (kern, maxabs(out.cpu(), exact))
+        assert maxabs(out, one) <= TOL_F16
+        assert maxabs(lse, lse_one) <= 2e-3
+    auto = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale)       # automatic split
+    assert maxabs(auto.cpu(), exact) <= TOL_F16
+    assert fst.last_status() == 0
