@@ -131,7 +131,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     const int g = lane >> 2, t = lane & 3;
     const int row0 = b * BM;
     const int prefix = a.prefix, n_q = a.n_q;
-    const uint32_t bar_qk = s_base + SM::BAR, bar_v = bar_qk + 8;
+    const uint32_t bar_qk = s_base + SM::BAR, bar_v = bar_qk + 8, bar_p = bar_qk + 16;   // bar_p: one per stage
     // With the prefix split over several CTAs, split 0 also owns the tree part (block rows and
     // external ancestors); every split takes a contiguous run of prefix tiles.
     const bool tree = split == 0;
@@ -169,6 +169,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     if (tid == 0) {
         mbar_init(bar_qk, 1);
         mbar_init(bar_v, 1);
+        mbar_init(bar_p, 1);
+        mbar_init(bar_p + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         mbar_arrive_expect_tx(bar_qk, (tree ? 2 : 1) * NB32 * SM::TILE);
 #pragma unroll
@@ -189,27 +191,34 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         }
     }
 
-    // ---- gathered tiles (cp.async into the swizzled layout): external ancestors, then prefix
+    // ---- gathered tiles.  External ancestors: cp.async row by row into the swizzled layout (all
+    //      threads).  Prefix tiles are dense: thread 0 fetches them as TMA boxes onto the stage's
+    //      mbarrier; rows past this CTA's share of the prefix arrive too and are masked off.
     auto load_gathered = [&](int e, int st, bool ext, const int (&node)[SPT]) {
         const uint32_t kd = s_base + (st ? SM::ST1 : SM::ST0);
         const uint32_t vd = kd + TP * SM::TILE;
+        if (ext) {
 #pragma unroll
-        for (int j = 0; j < SPT; ++j) {
-            const int s = lr + j * RPP;
-            long long rr = 0;
-            bool ok;
-            if (ext) {
-                ok = node[j] >= 0 && node[j] < n_q;
+            for (int j = 0; j < SPT; ++j) {
+                const int s = lr + j * RPP;
+                const bool ok = node[j] >= 0 && node[j] < n_q;
                 if (node[j] >= n_q) report(a.status, FST_DEV_INDEX_RANGE, b, e * TN + s);
-                if (ok) rr = prefix + node[j];
-            } else {
-                const int p = p_lo + (e - nt_ext_of<TN>(count, a.ma)) * TN + s;
-                ok = p < p_end;
-                if (ok) rr = p;
+                const long long rr = ok ? prefix + node[j] : 0;
+                const uint32_t o = (s >> 5) * SM::TILE + TL::off(s & 31, lc);
+                cp_async16(kd + o, kp + rr * a.ks_n + lc * 8, ok);
+                cp_async16(vd + o, vp + rr * a.vs_n + lc * 8, ok);
             }
-            const uint32_t o = (s >> 5) * SM::TILE + TL::off(s & 31, lc);
-            cp_async16(kd + o, kp + rr * a.ks_n + lc * 8, ok);
-            cp_async16(vd + o, vp + rr * a.vs_n + lc * 8, ok);
+        } else if (tid == 0) {
+            const int p0 = p_lo + (e - nt_ext_of<TN>(count, a.ma)) * TN;
+            const uint32_t bar = bar_p + st * 8;
+            mbar_arrive_expect_tx(bar, 2 * TP * SM::TILE);
+#pragma unroll
+            for (int tp = 0; tp < TP; ++tp)
+#pragma unroll
+                for (int hf = 0; hf < TL::HALVES; ++hf) {
+                    tma_load_4d(kd + tp * SM::TILE + hf * 4096, &tm_k, hf * 64, p0 + tp * 32, h, z, bar);
+                    tma_load_4d(vd + tp * SM::TILE + hf * 4096, &tm_v, hf * 64, p0 + tp * 32, h, z, bar);
+                }
         }
     };
     // without a prefix the first gathered tile is requested before the count has arrived
@@ -283,10 +292,15 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             kbase = s_base + SM::KB + i * TP * SM::TILE;
             vbase = s_base + SM::VB + i * TP * SM::TILE;
         } else {
-            kbase = s_base + ((e & 1) ? SM::ST1 : SM::ST0);
+            const int st = e & 1;
+            kbase = s_base + (st ? SM::ST1 : SM::ST0);
             vbase = kbase + TP * SM::TILE;
-            cp_async_wait<1>();
-            __syncthreads();
+            if (e < nt_ext) {
+                cp_async_wait<1>();
+                __syncthreads();
+            } else {                                      // k-th TMA use of this stage: parity k & 1
+                alive = mbar_wait(bar_p + st * 8, ((e - nt_ext) >> 1) & 1, a.status, b) && alive;
+            }
         }
         // 16-column groups any of my warp's 16 rows use
         bool act[NG];
