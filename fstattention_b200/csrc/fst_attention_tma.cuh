@@ -102,7 +102,9 @@ struct TmaSmem {
     static constexpr int BYTES = BAR + 64 + 1024;         // + slack to align the base to 1 KB
 };
 
-template <typename T, int D, int BM, int TN>
+// PFX = false compiles the shared-prefix machinery (dense tiles, split over CTAs) out: the
+// no-prefix kernel is smaller, and for a latency-bound kernel fewer instruction bytes is time.
+template <typename T, int D, int BM, int TN, bool PFX>
 __global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : 1))
 attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -126,16 +128,17 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     extern __shared__ unsigned char smem_raw[];
     const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;    // swizzle atoms are 1 KB
     const int b = blockIdx.x, h = blockIdx.y;
-    const int z = blockIdx.z / a.n_splits, split = blockIdx.z - z * a.n_splits;
+    const int n_splits = PFX ? a.n_splits : 1;
+    const int z = blockIdx.z / n_splits, split = blockIdx.z - z * n_splits;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row0 = b * BM;
-    const int prefix = a.prefix, n_q = a.n_q;
+    const int prefix = PFX ? a.prefix : 0, n_q = a.n_q;
     const uint32_t bar_qk = s_base + SM::BAR, bar_v = bar_qk + 8, bar_p = bar_qk + 16;   // bar_p: one per stage
     // With the prefix split over several CTAs, split 0 also owns the tree part (block rows and
     // external ancestors); every split takes a contiguous run of prefix tiles.
     const bool tree = split == 0;
-    const int pt_total = (prefix + TN - 1) / TN, pt_per = (pt_total + a.n_splits - 1) / a.n_splits;
+    const int pt_total = (prefix + TN - 1) / TN, pt_per = (pt_total + n_splits - 1) / n_splits;
     const int pt_lo = min(split * pt_per, pt_total), pt_hi = min(pt_lo + pt_per, pt_total);
     const int p_lo = pt_lo * TN, p_end = min(prefix, pt_hi * TN);      // my prefix rows [p_lo, p_end)
     const int nblk = tree ? SM::NBT : 0;
@@ -305,6 +308,10 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         // 16-column groups any of my warp's 16 rows use
         bool act[NG];
         bool any = false;
+        uint32_t all_bits = 0xffffffffu;
+#pragma unroll
+        for (int p = 0; p < TP; ++p) all_bits &= w0[p] & w1[p];
+        const bool dense = PFX && __reduce_and_sync(0xffffffffu, all_bits) == 0xffffffffu;   // every row, every column
 #pragma unroll
         for (int p = 0; p < TP; ++p) {
             const uint32_t occ = __reduce_or_sync(0xffffffffu, w0[p] | w1[p]);
@@ -334,17 +341,25 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             }
             // ---- mask, running max (raw units), probabilities
             float mx0 = -INFINITY, mx1 = -INFINITY;
+            if (dense) {                                  // a full prefix tile: nothing to mask
 #pragma unroll
-            for (int n = 0; n < 2 * NG; ++n) {
-                if (act[n >> 1]) {
-                    const int c = (n & 3) * 8 + 2 * t;
-                    const uint32_t b0 = w0[n >> 2] >> c, b1 = w1[n >> 2] >> c;
-                    s[n][0] = (b0 & 1u) ? s[n][0] : -INFINITY;
-                    s[n][1] = (b0 & 2u) ? s[n][1] : -INFINITY;
-                    s[n][2] = (b1 & 1u) ? s[n][2] : -INFINITY;
-                    s[n][3] = (b1 & 2u) ? s[n][3] : -INFINITY;
+                for (int n = 0; n < 2 * NG; ++n) {
                     mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
                     mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < 2 * NG; ++n) {
+                    if (act[n >> 1]) {
+                        const int c = (n & 3) * 8 + 2 * t;
+                        const uint32_t b0 = w0[n >> 2] >> c, b1 = w1[n >> 2] >> c;
+                        s[n][0] = (b0 & 1u) ? s[n][0] : -INFINITY;
+                        s[n][1] = (b0 & 2u) ? s[n][1] : -INFINITY;
+                        s[n][2] = (b1 & 1u) ? s[n][2] : -INFINITY;
+                        s[n][3] = (b1 & 2u) ? s[n][3] : -INFINITY;
+                        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+                        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+                    }
                 }
             }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -419,7 +434,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = (l0 > 0.f && alive) ? 1.f / l0 : 0.f, inv1 = (l1 > 0.f && alive) ? 1.f / l1 : 0.f;
-    if (a.n_splits > 1) {
+    if (PFX && n_splits > 1) {
         // partial result of this split: normalised rows in fp32 plus their log-sum-exp; the
         // combine kernel weighs the splits against each other
         const size_t prow = ((size_t(split) * a.Z + z) * a.H + h) * n_q + row0;
@@ -537,8 +552,8 @@ inline bool make_map(CUtensorMap *map, const void *base, bool bf16, int D, int r
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, int D, int BM, int TN>
-cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
+template <typename T, int D, int BM, int TN, bool PFX>
+cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
     using SM = TmaSmem<D, BM, TN>;
     constexpr size_t smem = SM::BYTES;
     constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
@@ -550,19 +565,25 @@ cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
         return cudaErrorNotSupported;
     static bool configured = false;                       // one process drives one device
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN>,
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
         configured = true;
     }
     if (a.n_splits < 1 || (long long)a.Z * a.n_splits > 65535) return cudaErrorInvalidValue;
     dim3 grid(a.nb, a.H, a.Z * a.n_splits), block(BM * 2);
-    attn_tma_kernel<T, D, BM, TN><<<grid, block, smem, stream>>>(a, tq, tk, tv, to);
+    attn_tma_kernel<T, D, BM, TN, PFX><<<grid, block, smem, stream>>>(a, tq, tk, tv, to);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess || a.n_splits == 1) return e;
     const size_t items = size_t(a.Z) * a.H * a.n_q * (D / 4);
     combine_splits_kernel<T, D><<<unsigned((items + 127) / 128), 128, 0, stream>>>(a);
     return cudaGetLastError();
+}
+
+template <typename T, int D, int BM, int TN>
+cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
+    return a.prefix > 0 ? launch_tma_pfx<T, D, BM, TN, true>(a, stream)
+                        : launch_tma_pfx<T, D, BM, TN, false>(a, stream);
 }
 
 // tile_cols: 32, 64, or 0 = by grid size: 64-column tiles up to about eight CTAs per SM (measured:
