@@ -398,12 +398,14 @@ template <typename T, int D, int BM>
 cudaError_t launch_mma_inst(const AttnArgs &a, cudaStream_t stream) {
     using SM = MmaSmem<D, BM>;
     constexpr size_t smem = SM::BYTES;
-    static bool configured = false;                       // one process drives one device
-    if (!configured) {
+    static bool configured_on[kMaxDevices] = {};           // the attribute is per device
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (!configured_on[slot]) {
         cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<T, D, BM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured_on[slot] = true;
     }
     dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
     attn_mma_kernel<T, D, BM><<<grid, block, smem, stream>>>(a);

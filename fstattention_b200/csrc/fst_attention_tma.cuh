@@ -563,12 +563,14 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
         !make_map(&tv, a.v, bf16, D, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
         !make_map(&to, a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z))
         return cudaErrorNotSupported;
-    static bool configured = false;                       // one process drives one device
-    if (!configured) {
+    static bool configured_on[kMaxDevices] = {};           // the attribute is per device
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (!configured_on[slot]) {
         cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured_on[slot] = true;
     }
     if (a.n_splits < 1 || (long long)a.Z * a.n_splits > 65535) return cudaErrorInvalidValue;
     dim3 grid(a.nb, a.H, a.Z * a.n_splits), block(BM * 2);

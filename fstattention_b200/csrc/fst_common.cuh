@@ -45,6 +45,15 @@ __device__ inline void report(int32_t *status, int code, int where, int detail) 
     }
 }
 
+// Index of the current device, for per-device caches of launch configuration (a function
+// attribute set on one device says nothing about another).  -1 when it cannot be told.
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+
 // Kernel launchers (defined in the .cu files, called from fst_api.cu)
 cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
                               int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,

@@ -366,7 +366,7 @@ pack_kernel(const int64_t *__restrict__ anc_idx_all, const uint8_t *__restrict__
     }
 }
 
-static size_t g_pre_smem_set = 48 * 1024;
+static size_t g_pre_smem_set[kMaxDevices] = {};       // largest dynamic shared memory enabled, per device
 
 cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
                               int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,
@@ -386,11 +386,13 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
     const size_t cap = (budget - fixed) / 4;
     const int par_cap = int(cap < size_t(n_nodes) ? cap : size_t(n_nodes));
     const size_t smem = fixed + size_t(par_cap) * 4;
-    if (smem > g_pre_smem_set) {
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (smem > 48 * 1024 && smem > g_pre_smem_set[slot]) {
         cudaError_t e = cudaFuncSetAttribute(precompute_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        g_pre_smem_set = smem;
+        g_pre_smem_set[slot] = smem;
     }
     dim3 grid(nb, n_trees);
     precompute_kernel<<<grid, PRE_THREADS, smem, stream>>>(
