@@ -293,3 +293,23 @@ def test_prefix_split_over_ctas(fst, prefix, splits):
     auto = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale)       # automatic split
     assert maxabs(auto.cpu(), exact) <= TOL_F16
     assert fst.last_status() == 0
+
+
+def test_dfs_renumbering_leaves_the_result_unchanged(fst):
+    """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
+    attention on the original numbering (and the oracle), while gathering fewer rows."""
+    from fstattention_b200 import configs
+    par = configs.random_window_tree(9, 700, 200)       # wide window: ancestors far away in index space
+    n, H, D = len(par), 2, 128
+    q, k, v = make_qkv(1, H, n, n, D, torch.float16, seed=31)
+    scale = D ** -0.5
+    exact = oracle_attention(q, k, v, par, scale, compute_dtype=torch.float32)
+    order, new_par = fst.dfs_order(par)
+    idx = torch.tensor(order)
+    meta = fst.build_tree_metadata(new_par, 64, 512)
+    o_perm = fst.fst_attention(q[:, :, idx].cuda(), k[:, :, idx].cuda(), v[:, :, idx].cuda(), meta, sm_scale=scale)
+    out = torch.empty_like(o_perm)
+    out[:, :, idx.cuda()] = o_perm
+    assert maxabs(out.cpu(), exact) <= TOL_F16
+    before = fst.build_tree_metadata(par, 64, 700)
+    assert int(meta.packed.view(torch.int32)[0, :meta.n_blocks].sum()) < int(before.packed.view(torch.int32)[0, :before.n_blocks].sum())

@@ -109,3 +109,53 @@ def test_create_tree_and_full_mask_match_reference(metadata_golden):
         assert np.array_equal(got.numpy(), ref), name
         seen += 1
     assert seen >= 5
+
+
+def _gathered_rows(parent, bm):
+    total = 0
+    for lo in range(0, len(parent), bm):
+        anc = set()
+        rows = range(lo, min(lo + bm, len(parent)))
+        for k in rows:
+            x = parent[k]
+            while x >= 0 and x not in anc:
+                anc.add(x)
+                x = parent[x]
+        total += len(anc) + sum(1 for k in rows if k not in anc)
+    return total
+
+
+def test_dfs_order_is_a_valid_renumbering_and_shrinks_the_gather():
+    import fstattention_b200 as fst
+    from fstattention_b200 import configs
+    deep = configs.deep_chain_tree(0, 4096, chains=64)          # 2579 nodes, construction order
+    # breadth-first numbering of the same tree: the bad case
+    children = [[] for _ in deep]
+    for i, p in enumerate(deep):
+        if p >= 0:
+            children[p].append(i)
+    bfs = [0]
+    for x in bfs:
+        bfs.extend(children[x])
+    new_of = {old: new for new, old in enumerate(bfs)}
+    bfs_parent = [-1 if deep[old] < 0 else new_of[deep[old]] for old in bfs]
+    for par in (bfs_parent, deep, configs.random_window_tree(1, 500), [-1, -1, 0, 1, 0, -1, 5]):
+        order, new_parent = fst.dfs_order(par)
+        n = len(par)
+        assert sorted(order) == list(range(n))
+        assert all(p < i for i, p in enumerate(new_parent))
+        pos = {old: new for new, old in enumerate(order)}
+        for new, old in enumerate(order):                        # same tree, renamed
+            assert new_parent[new] == (-1 if par[old] < 0 else pos[par[old]])
+        # pre-order: every subtree is a contiguous run starting at its root
+        last = list(range(n))
+        for i in range(n - 1, -1, -1):
+            if new_parent[i] >= 0:
+                last[new_parent[i]] = max(last[new_parent[i]], last[i])
+        size = [1] * n
+        for i in range(n - 1, -1, -1):
+            if new_parent[i] >= 0:
+                size[new_parent[i]] += size[i]
+        assert all(last[i] == i + size[i] - 1 for i in range(n))
+    order, dfs_parent = fst.dfs_order(bfs_parent)
+    assert _gathered_rows(dfs_parent, 64) * 5 < _gathered_rows(bfs_parent, 64)
