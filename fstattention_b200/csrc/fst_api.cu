@@ -8,6 +8,18 @@ cudaError_t launch_mma_f16_d64(const AttnArgs &, int, cudaStream_t);
 cudaError_t launch_mma_f16_d128(const AttnArgs &, int, cudaStream_t);
 cudaError_t launch_mma_bf16_d64(const AttnArgs &, int, cudaStream_t);
 cudaError_t launch_mma_bf16_d128(const AttnArgs &, int, cudaStream_t);
+cudaError_t launch_combine_f16_d64(const AttnArgs &, cudaStream_t);
+cudaError_t launch_combine_f16_d128(const AttnArgs &, cudaStream_t);
+cudaError_t launch_combine_bf16_d64(const AttnArgs &, cudaStream_t);
+cudaError_t launch_combine_bf16_d128(const AttnArgs &, cudaStream_t);
+
+cudaError_t launch_combine(const AttnArgs &a, int dtype, cudaStream_t stream) {
+    if (dtype == FST_F16 && a.D == 64) return launch_combine_f16_d64(a, stream);
+    if (dtype == FST_F16 && a.D == 128) return launch_combine_f16_d128(a, stream);
+    if (dtype == FST_BF16 && a.D == 64) return launch_combine_bf16_d64(a, stream);
+    if (dtype == FST_BF16 && a.D == 128) return launch_combine_bf16_d128(a, stream);
+    return cudaErrorNotSupported;
+}
 
 cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream) {
     if (dtype == FST_F16 && a.D == 64) return launch_mma_f16_d64(a, variant, stream);
@@ -120,8 +132,8 @@ int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
 }
 
 size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, int kv_splits) {
-    if (Z <= 0 || H <= 0 || n_q <= 0 || head_dim <= 0 || kv_splits <= 1) return 0;
-    return size_t(kv_splits) * Z * H * n_q * (size_t(head_dim) + 1) * sizeof(float);
+    if (Z <= 0 || H <= 0 || n_q <= 0 || head_dim <= 0 || kv_splits < 1) return 0;
+    return size_t(kv_splits + 1) * Z * H * n_q * (size_t(head_dim) + 1) * sizeof(float);
 }
 
 static int attention_fwd_impl(const void *q, const void *k, const void *v, void *o, float *lse,
@@ -156,6 +168,8 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     a.n_splits = 1;
     a.part_o = nullptr;
     a.part_lse = nullptr;
+    a.skip_prefix = 0;
+    a.part_slots = 1;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // the tensor-core kernel moves 16-byte pieces: every row must start on a 16-byte boundary
@@ -171,26 +185,42 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (automatic)
         choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_TMA : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice != FST_KERNEL_MMA && choice != FST_KERNEL_TMA && choice != FST_KERNEL_TMA_T32 &&
-        choice != FST_KERNEL_TMA_T64)
-        return FST_ERR_INVALID_ARG;
+    if (choice < FST_KERNEL_MMA || choice > FST_KERNEL_TMA_UMMA) return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
-    if (kv_splits > 1 && a.prefix > 0 && choice != FST_KERNEL_MMA) {
-        // the prefix is cut into kv_splits runs of tiles; partial results go through the workspace
+
+    // A shared prefix with a workspace: either the tcgen05 prefix kernel takes it in kv_splits runs
+    // while the tree kernel does the tree part (head_dim 128; chosen automatically from 256
+    // prefix rows on), or the tree kernel itself is launched kv_splits times over the prefix.
+    const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA;
+    const bool want_umma = can_part && head_dim == 128 &&
+                           (choice == FST_KERNEL_TMA_UMMA || (automatic && a.prefix >= 256));
+    if (choice == FST_KERNEL_TMA_UMMA && !want_umma) return FST_ERR_UNSUPPORTED;
+    if (can_part && (want_umma || kv_splits > 1)) {
         const size_t need = fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits);
-        if (!workspace || workspace_bytes < need) return FST_ERR_WORKSPACE;
+        if (workspace_bytes < need) return FST_ERR_WORKSPACE;
         if (!aligned16(workspace)) return FST_ERR_ALIGNMENT;
-        a.n_splits = kv_splits;
+        a.part_slots = want_umma ? kv_splits + 1 : kv_splits;
         a.part_o = static_cast<float *>(workspace);
-        a.part_lse = a.part_o + size_t(kv_splits) * Z * H * n_q * head_dim;
+        a.part_lse = a.part_o + size_t(a.part_slots) * Z * H * n_q * head_dim;
+        cudaError_t e;
+        if (want_umma) {
+            a.skip_prefix = 1;
+            e = launch_attention_mma(a, dtype, FST_KERNEL_TMA, st);
+            if (e == cudaSuccess) e = launch_prefix_umma(a, dtype, kv_splits, 1, st);
+        } else {
+            a.n_splits = kv_splits;
+            e = launch_attention_mma(a, dtype, choice, st);
+        }
+        if (e == cudaSuccess) e = launch_combine(a, dtype, st);
+        if (e != cudaErrorNotSupported || !automatic) return cuda_status(e);
+        a.n_splits = 1;                                   // a tensor map could not be built: fall through
+        a.skip_prefix = 0;
+        a.part_slots = 1;
     }
-    cudaError_t e = launch_attention_mma(a, dtype, choice, st);
+    cudaError_t e = launch_attention_mma(a, dtype, choice == FST_KERNEL_TMA_UMMA ? FST_KERNEL_TMA : choice, st);
     // shapes or strides the TMA variant cannot describe fall back to the cp.async variant
-    if (e == cudaErrorNotSupported && automatic) {
-        a.n_splits = 1;
-        e = launch_attention_mma(a, dtype, FST_KERNEL_MMA, st);
-    }
+    if (e == cudaErrorNotSupported && automatic) e = launch_attention_mma(a, dtype, FST_KERNEL_MMA, st);
     return cuda_status(e);
 }
 

@@ -8,4 +8,7 @@ cudaError_t launch_mma_bf16_d64(const AttnArgs &a, int variant, cudaStream_t str
     if (variant == FST_KERNEL_TMA_T64) return launch_tma_d<__nv_bfloat16, 64>(a, 64, stream);
     return launch_mma_d<__nv_bfloat16, 64>(a, variant, stream);
 }
+cudaError_t launch_combine_bf16_d64(const AttnArgs &a, cudaStream_t stream) {
+    return launch_combine_t<__nv_bfloat16, 64>(a, stream);
+}
 }  // namespace fst

@@ -138,7 +138,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     // With the prefix split over several CTAs, split 0 also owns the tree part (block rows and
     // external ancestors); every split takes a contiguous run of prefix tiles.
     const bool tree = split == 0;
-    const int pt_total = (prefix + TN - 1) / TN, pt_per = (pt_total + n_splits - 1) / n_splits;
+    const int pt_total = (PFX && a.skip_prefix) ? 0 : (prefix + TN - 1) / TN, pt_per = (pt_total + n_splits - 1) / n_splits;
     const int pt_lo = min(split * pt_per, pt_total), pt_hi = min(pt_lo + pt_per, pt_total);
     const int p_lo = pt_lo * TN, p_end = min(prefix, pt_hi * TN);      // my prefix rows [p_lo, p_end)
     const int nblk = tree ? SM::NBT : 0;
@@ -434,7 +434,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = (l0 > 0.f && alive) ? 1.f / l0 : 0.f, inv1 = (l1 > 0.f && alive) ? 1.f / l1 : 0.f;
-    if (PFX && n_splits > 1) {
+    if (PFX && (n_splits > 1 || a.skip_prefix)) {
         // partial result of this split: normalised rows in fp32 plus their log-sum-exp; the
         // combine kernel weighs the splits against each other
         const size_t prow = ((size_t(split) * a.Z + z) * a.H + h) * n_q + row0;
@@ -494,10 +494,10 @@ combine_splits_kernel(const AttnArgs a) {
     const int c = int(idx - row * CPR) * 4;
     if (row >= rows) return;
     float big = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) big = fmaxf(big, a.part_lse[size_t(s) * rows + row]);
+    for (int s = 0; s < a.part_slots; ++s) big = fmaxf(big, a.part_lse[size_t(s) * rows + row]);
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    for (int s = 0; s < a.n_splits; ++s) {
+    for (int s = 0; s < a.part_slots; ++s) {
         const float ls = a.part_lse[size_t(s) * rows + row];
         if (ls == -INFINITY) continue;
         const float w = exp2f(ls - big);
@@ -515,6 +515,13 @@ combine_splits_kernel(const AttnArgs a) {
     packed.y = MmaTraits<T>::pack(sum.z * inv, sum.w * inv);
     *reinterpret_cast<uint2 *>(op) = packed;
     if (a.lse != nullptr && c == 0) a.lse[row] = big + log2f(wsum);
+}
+
+template <typename T, int D>
+cudaError_t launch_combine_t(const AttnArgs &a, cudaStream_t stream) {
+    const size_t items = size_t(a.Z) * a.H * a.n_q * (D / 4);
+    combine_splits_kernel<T, D><<<unsigned((items + 127) / 128), 128, 0, stream>>>(a);
+    return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -575,10 +582,6 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
     if (a.n_splits < 1 || (long long)a.Z * a.n_splits > 65535) return cudaErrorInvalidValue;
     dim3 grid(a.nb, a.H, a.Z * a.n_splits), block(BM * 2);
     attn_tma_kernel<T, D, BM, TN, PFX><<<grid, block, smem, stream>>>(a, tq, tk, tv, to);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess || a.n_splits == 1) return e;
-    const size_t items = size_t(a.Z) * a.H * a.n_q * (D / 4);
-    combine_splits_kernel<T, D><<<unsigned((items + 127) / 128), 128, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

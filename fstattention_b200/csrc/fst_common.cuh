@@ -80,10 +80,18 @@ struct AttnArgs {
     int n_splits;
     float *part_o;
     float *part_lse;
+    // skip_prefix: the tree kernel leaves the prefix to the tcgen05 prefix kernel and writes its
+    // own result as partial slot 0; part_slots: how many partial slots the merge kernel reads
+    int skip_prefix;
+    int part_slots;
 };
 
 cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);
 // returns cudaErrorNotSupported when no tensor-core instantiation fits
 cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream);
+// dense prefix on tcgen05: partial results of n_runs runs into slots first_slot..; D = 128 only
+cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream);
+// merge a.part_slots partial results into o (and lse)
+cudaError_t launch_combine(const AttnArgs &a, int dtype, cudaStream_t stream);
 
 }  // namespace fst

@@ -1,0 +1,338 @@
+// Dense attention over the shared prefix on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// The prefix part of the reference kernel (fstattention.py:113-136) is plain dense attention:
+// every query row attends to every prefix row.  That is the one place on this path where the
+// tiles are large and dense, so it gets its own kernel: one CTA per (128 query rows, head,
+// batch element, run of prefix rows).  Per 128-row K/V tile
+//     S = Q K^T     tcgen05.mma  M=128 N=128 K=16 x 8, both operands K-major in shared memory
+//     softmax       one thread per query row (TMEM lane = row, so no shuffles): tcgen05.ld of S,
+//                   running maximum with a lazy reference point, P written to shared memory
+//     O += P V      tcgen05.mma  A = P (K-major), B = V (MN-major: rows of V are the K index)
+// with S (128 columns) and O (128 columns) living in tensor memory.  K/V tiles arrive by TMA
+// (128-row x 64-column boxes, 128-byte swizzle) into two stages.  The result is a partial
+// output per run (normalised rows in fp32 plus base-2 log-sum-exp) in the layout the tree
+// kernel writes; combine_splits_kernel merges them.
+//
+// One thread issues TMA and MMA; all 128 threads do the softmax.  Every wait is bounded in time
+// (mbar_wait): on expiry the kernel records FST_DEV_TIMEOUT, stops issuing, frees its tensor
+// memory and returns.
+
+#include "fst_attention_tma.cuh"
+
+namespace fst {
+
+namespace umma {
+
+constexpr int D = 128;                 // head dimension this kernel is built for
+constexpr int QM = 128;                // query rows per CTA (MMA M)
+constexpr int KN = 128;                // K/V rows per tile (MMA N of the first product)
+constexpr int HALF = QM * 128;         // bytes of one 64-column half of a 128-row tile
+constexpr int TILE = 2 * HALF;         // bytes of a 128 x 128 fp16 tile
+constexpr int OFF_Q = 0;
+constexpr int OFF_P = OFF_Q + TILE;
+constexpr int OFF_K = OFF_P + TILE;    // two stages
+constexpr int OFF_V = OFF_K + 2 * TILE;
+constexpr int OFF_BAR = OFF_V + 2 * TILE;
+constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;   // + barriers, TMEM address, 1 KB alignment slack
+
+// shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1 KB apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((addr >> 4) & 0x3fff);                 // start address
+    d |= uint64_t((lbo_bytes >> 4) & 0x3fff) << 16;      // leading byte offset
+    d |= uint64_t((1024 >> 4) & 0x3fff) << 32;           // stride byte offset
+    d |= uint64_t(1) << 46;                              // descriptor version (Blackwell)
+    d |= uint64_t(2) << 61;                              // SWIZZLE_128B
+    return d;
+}
+
+// instruction descriptor: f32 accumulate, M=128, N=128, A K-major, B K- or MN-major
+__device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(b_mn_major) << 16) |
+           (uint32_t(KN >> 3) << 17) | (uint32_t(QM >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        bool accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32"
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+                 " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
+                 " %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+}  // namespace umma
+
+// Arguments of the prefix kernel beyond AttnArgs: where this launch's partial results start.
+struct PrefixArgs {
+    int n_runs;          // runs of prefix rows (CTAs per query tile, head, batch element)
+    int first_slot;      // partial-result slot of run 0 (slot 0 belongs to the tree kernel)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128, 1)
+prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant__ CUtensorMap tm_q,
+                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+    using namespace umma;
+    using MT = MmaTraits<T>;
+    constexpr bool BF16 = !std::is_same<T, __half>::value;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem = smem_raw + (s_base - smem_u32(smem_raw));
+    const int qt = blockIdx.x, h = blockIdx.y;
+    const int z = blockIdx.z / pa.n_runs, run = blockIdx.z - z * pa.n_runs;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int prefix = a.prefix, n_q = a.n_q;
+    const int row = qt * QM + tid;                        // my query row (TMEM lane tid)
+
+    // my run of prefix rows, in whole tiles
+    const int tiles_total = (prefix + KN - 1) / KN, per = (tiles_total + pa.n_runs - 1) / pa.n_runs;
+    const int t_lo = min(run * per, tiles_total), t_hi = min(t_lo + per, tiles_total);
+    const int nt = t_hi - t_lo;
+    const int p_lo = t_lo * KN, p_end = min(prefix, t_hi * KN);
+
+    const uint32_t bar_q = s_base + OFF_BAR, bar_kv = bar_q + 8 /* two */, bar_s = bar_q + 24, bar_o = bar_q + 32;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 64);
+
+    if (tid == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(bar_kv, 1);
+        mbar_init(bar_kv + 8, 1);
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {                                      // 256 columns of tensor memory: S and O
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;  // this warp's 32 TMEM lanes
+
+    auto load_kv = [&](int t, int st) {                   // thread 0: K and V tile t of my run
+        const uint32_t bar = bar_kv + st * 8;
+        mbar_arrive_expect_tx(bar, 2 * TILE);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            tma_load_4d(s_base + OFF_K + st * TILE + hf * HALF, &tm_k, hf * 64, p_lo + t * KN, h, z, bar);
+            tma_load_4d(s_base + OFF_V + st * TILE + hf * HALF, &tm_v, hf * 64, p_lo + t * KN, h, z, bar);
+        }
+    };
+    if (tid == 0 && nt > 0) {
+        mbar_arrive_expect_tx(bar_q, TILE);
+        tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
+        tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
+        load_kv(0, 0);
+        if (nt > 1) load_kv(1, 1);
+    }
+
+    const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
+    const float c2 = a.scale_log2;
+    float m_ref = -INFINITY, l = 0.f;                     // reference point of the exponent, row sum
+    bool alive = true;
+
+    auto issue_s = [&](int t) {                           // thread 0: S = Q K^T for tile t
+        const int st = t & 1;
+        if (t == 0) alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
+        alive = mbar_wait(bar_kv + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+        if (!alive) return;
+        umma::fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t koff = (ks >> 2) * HALF + (ks & 3) * 32;
+            mma_f16(tmem_s, smem_desc(s_base + OFF_Q + koff, 16), smem_desc(s_base + OFF_K + st * TILE + koff, 16),
+                    idesc_s, ks > 0);
+        }
+        mma_commit(bar_s);
+    };
+    if (tid == 0 && nt > 0) issue_s(0);
+
+#pragma unroll 1
+    for (int t = 0; t < nt; ++t) {
+        const int st = t & 1;
+        alive = mbar_wait(bar_s, t & 1, a.status, qt) && alive;
+        // every thread must stay in step (the TMEM loads below are warp-wide), so a dead wait
+        // only poisons the result; thread 0 stops issuing
+        umma::fence_after_sync();
+        const int cols = min(KN, p_end - (p_lo + t * KN));       // valid columns of this tile
+
+        // ---- pass 1: row maximum
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c0 = 0; c0 < KN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(r, tmem_s + lane_base + c0);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c0 + i < cols) ? __uint_as_float(r[i]) : -INFINITY);
+        }
+        // the reference point moves only when the maximum grows by more than 2^8
+        const bool up = (mx - m_ref) * c2 > 8.f;          // true from -inf
+        if (__any_sync(0xffffffffu, up) && t > 0) {       // rescale O in tensor memory (rare)
+            const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(r, tmem_o + lane_base + c0);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                tmem_st32(tmem_o + lane_base + c0, r);
+            }
+            l *= alpha;
+        }
+        if (up) m_ref = mx;
+        const float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
+
+        // ---- pass 2: probabilities, row sum, P into shared memory (K-major, swizzled)
+        unsigned char *prow = smem + OFF_P + tid * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < KN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(r, tmem_s + lane_base + c0);
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float p0 = (c0 + i < cols) ? fast_exp2(fmaf(__uint_as_float(r[i]), c2, -mu)) : 0.f;
+                const float p1 = (c0 + i + 1 < cols) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), c2, -mu)) : 0.f;
+                l += p0 + p1;
+                packed[i >> 1] = MT::pack(p0, p1);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {              // four 16-byte chunks of my row
+                const int chunk = (c0 >> 3) + q4;         // 0..15 across the row
+                unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2],
+                                                             packed[q4 * 4 + 3]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P visible to the tensor core
+        umma::fence_before_sync();
+        __syncthreads();
+
+        if (tid == 0 && alive) {
+            umma::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < KN / 16; ++ks) {        // O += P V, 16 prefix rows per step
+                const uint32_t aoff = (ks >> 2) * HALF + (ks & 3) * 32;
+                mma_f16(tmem_o, smem_desc(s_base + OFF_P + aoff, 16),
+                        smem_desc(s_base + OFF_V + st * TILE + ks * 16 * 128, HALF), idesc_pv, t > 0 || ks > 0);
+            }
+            mma_commit(bar_o);
+            if (t + 1 < nt) issue_s(t + 1);               // queued behind the product above
+            if (t + 2 < nt) {                             // stage st is free once O += P V has read it
+                alive = mbar_wait(bar_o, t & 1, a.status, qt) && alive;
+                if (alive) load_kv(t + 2, st);
+            }
+        }
+    }
+
+    // ---- epilogue: O / l and the log-sum-exp of my row into this run's partial-result slot
+    if (nt > 0) alive = mbar_wait(bar_o, (nt - 1) & 1, a.status, qt) && alive;
+    umma::fence_after_sync();
+    const size_t slot = size_t(pa.first_slot + run);
+    const size_t prow = ((slot * a.Z + z) * a.H + h) * n_q + row;
+    const float inv = (l > 0.f && alive) ? 1.f / l : 0.f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        if (nt > 0) {
+            tmem_ld32(r, tmem_o + lane_base + c0);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row < n_q) {
+            float4 *dst = reinterpret_cast<float4 *>(a.part_o + prow * D + c0);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                dst[i >> 2] = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                          __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+        }
+    }
+    if (row < n_q) a.part_lse[prow] = (l > 0.f && alive) ? m_ref * c2 + log2f(l) : -INFINITY;
+
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256) : "memory");
+}
+
+// rank-4 map with 64-column x 128-row boxes
+static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int rows, int H, int Z,
+                             int64_t stride_n, int64_t stride_h, int64_t stride_z) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {cuuint64_t(umma::D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
+    const cuuint64_t strides[3] = {cuuint64_t(stride_n) * 2, cuuint64_t(stride_h) * 2, cuuint64_t(stride_z) * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T>
+static cudaError_t launch_prefix_t(const AttnArgs &a, int n_runs, int first_slot, cudaStream_t stream) {
+    constexpr bool bf16 = !std::is_same<T, __half>::value;
+    alignas(64) CUtensorMap tq, tk, tv;
+    if (!make_map_rows128(&tq, a.q, bf16, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
+        !make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+        !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z))
+        return cudaErrorNotSupported;
+    static bool configured_on[kMaxDevices] = {};
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (!configured_on[slot]) {
+        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             umma::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        configured_on[slot] = true;
+    }
+    if ((long long)a.Z * n_runs > 65535) return cudaErrorInvalidValue;
+    PrefixArgs pa{n_runs, first_slot};
+    dim3 grid((a.n_q + umma::QM - 1) / umma::QM, a.H, a.Z * n_runs);
+    prefix_umma_kernel<T><<<grid, 128, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
+    return cudaGetLastError();
+}
+
+// Partial results of the prefix, split into n_runs runs, into slots first_slot .. first_slot+n_runs-1.
+cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream) {
+    if (a.D != umma::D || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
+    if (dtype == FST_F16) return launch_prefix_t<__half>(a, n_runs, first_slot, stream);
+    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16>(a, n_runs, first_slot, stream);
+    return cudaErrorNotSupported;
+}
+
+}  // namespace fst

@@ -45,22 +45,32 @@ def _strides(t):
 _SMS = {}
 
 
-def _pick_splits(kv_splits, q, prefix, block_m, kernel) -> int:
-    """How many CTAs share one (block, head, batch)'s prefix.  Only the tensor-core kernels
-    split; the automatic choice aims at about four CTAs per SM and at least eight 64-row
-    tiles per split."""
+def _pick_splits(kv_splits, q, prefix, block_m, kernel):
+    """(runs the shared prefix is cut into, whether a workspace is needed).
+
+    Only the tensor-core kernels split.  With head_dim 128 and at least 256 prefix rows the
+    prefix goes to the tcgen05 kernel (one CTA per 128 query rows, head, batch element and run;
+    the automatic choice aims at two CTAs per SM, runs of at least 256 rows); otherwise the tree
+    kernel walks the prefix itself, split to about four CTAs per SM."""
     if q.dtype not in (torch.float16, torch.bfloat16) or q.shape[-1] not in (64, 128) \
             or block_m not in (32, 64, 128) or kernel in ("simt", "mma") or prefix <= 0:
-        return 1
-    if kv_splits is not None:
-        return max(1, int(kv_splits))
+        return 1, False
     dev = q.device
     sms = _SMS.get(dev)
     if sms is None:
         sms = _SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    z_cap = 65535 // max(q.shape[0], 1)
+    if q.shape[-1] == 128 and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
+        if kv_splits is not None:
+            return max(1, min(int(kv_splits), z_cap)), True
+        ctas = q.shape[0] * q.shape[1] * -(-q.shape[2] // 128)
+        return int(max(1, min((2 * sms) // max(ctas, 1), prefix // 256, z_cap))), True
+    if kv_splits is not None:
+        splits = max(1, min(int(kv_splits), z_cap))
+        return splits, splits > 1
     ctas = q.shape[0] * q.shape[1] * -(-q.shape[2] // block_m)
-    want = max(1, (4 * sms) // max(ctas, 1))
-    return int(max(1, min(want, prefix // 512, 65535 // max(q.shape[0], 1))))
+    splits = int(max(1, min((4 * sms) // max(ctas, 1), prefix // 512, z_cap)))
+    return splits, splits > 1
 
 
 def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_scale=None,
@@ -119,9 +129,9 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 raise ValueError("BLOCK_M / MAX_ANCESTORS differ from the ones the metadata was built with")
             if meta.n_blocks != -(-n_q // BLOCK_M):
                 raise ValueError("metadata block count does not match q")
-            splits = _pick_splits(kv_splits, q, n_kv - n_q, BLOCK_M, kernel)
+            splits, need_ws = _pick_splits(kv_splits, q, n_kv - n_q, BLOCK_M, kernel)
             ws, ws_bytes = None, 0
-            if splits > 1:
+            if need_ws:
                 ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, splits))
                 ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             rc = lib.fst_attention_fwd_splitkv(

@@ -51,7 +51,9 @@ enum fst_kernel {
     FST_KERNEL_TMA = 3,            /* same arithmetic, TMA tile loads + mbarriers, swizzled smem; */
                                    /* 32- or 64-column tiles chosen by grid size                 */
     FST_KERNEL_TMA_T32 = 4,        /* ... forced 32-column tiles (three CTAs per SM)             */
-    FST_KERNEL_TMA_T64 = 5         /* ... forced 64-column tiles (fewest softmax rounds)         */
+    FST_KERNEL_TMA_T64 = 5,        /* ... forced 64-column tiles (fewest softmax rounds)         */
+    FST_KERNEL_TMA_UMMA = 6        /* tree part as FST_KERNEL_TMA, shared prefix by the tcgen05  */
+                                   /* kernel (head_dim 128, fst_attention_fwd_splitkv only)      */
 };
 
 int fst_version(void);
@@ -142,7 +144,10 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * to fill the GPU (the reference walks the prefix in one program, fstattention.py:113-136).
  * Partial results (fp32) and their log-sum-exps pass through `workspace`
  * (fst_attention_split_workspace_bytes bytes, 16-byte aligned, scratch) and a second kernel merges
- * them.  kv_splits = 1, or no prefix, is fst_attention_fwd.  Tensor-core kernels only.
+ * them.  With head_dim 128 and at least 256 prefix rows FST_KERNEL_AUTO hands the prefix to a
+ * tcgen05/TMEM kernel (128 x 128 tiles, dense) in kv_splits runs and keeps the tree part in the
+ * tree kernel; FST_KERNEL_TMA_UMMA forces that, FST_KERNEL_TMA* forces the tree kernel to walk
+ * the prefix itself in kv_splits runs.  Without a prefix this is fst_attention_fwd.
  */
 size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, int kv_splits);
 int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void *o, float *lse,

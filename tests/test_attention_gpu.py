@@ -284,7 +284,7 @@ def test_prefix_split_over_ctas(fst, prefix, splits):
     scale = D ** -0.5
     exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
     one, lse_one = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kv_splits=1, return_lse=True)
-    for kern in ("tma_t32", "tma_t64", "auto"):
+    for kern in ("tma_t32", "tma_t64", "tma_umma", "auto"):
         out, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kv_splits=splits,
                                      return_lse=True, kernel=kern)
         assert maxabs(out.cpu(), exact) <= TOL_F16, (kern, maxabs(out.cpu(), exact))
