@@ -8,12 +8,13 @@
 //     softmax       one thread per query row (TMEM lane = row, so no shuffles): tcgen05.ld of S,
 //                   running maximum with a lazy reference point, P written to shared memory
 //     O += P V      tcgen05.mma  A = P (K-major), B = V (MN-major: rows of V are the K index)
-// with S (128 columns) and O (128 columns) living in tensor memory.  K/V tiles arrive by TMA
+// with S (two buffers of 128 columns) and O (128 columns) living in tensor memory.  K/V tiles arrive by TMA
 // (128-row x 64-column boxes, 128-byte swizzle) into two stages.  The result is a partial
 // output per run (normalised rows in fp32 plus base-2 log-sum-exp) in the layout the tree
 // kernel writes; combine_splits_kernel merges them.
 //
-// One thread issues TMA and MMA; all 128 threads do the softmax.  Every wait is bounded in time
+// A fifth warp's first lane issues TMA and MMA (S one tile ahead, into the other S buffer), the
+// four softmax warps talk to it through mbarriers only.  Every wait is bounded in time
 // (mbar_wait): on expiry the kernel records FST_DEV_TIMEOUT, stops issuing, frees its tensor
 // memory and returns.
 
@@ -95,8 +96,10 @@ struct PrefixArgs {
     int first_slot;      // partial-result slot of run 0 (slot 0 belongs to the tree kernel)
 };
 
+constexpr int PFX_THREADS = 160;       // four softmax warps (one thread per query row) + one control warp
+
 template <typename T>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(PFX_THREADS, 1)
 prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
     using namespace umma;
@@ -110,7 +113,6 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const int z = blockIdx.z / pa.n_runs, run = blockIdx.z - z * pa.n_runs;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int prefix = a.prefix, n_q = a.n_q;
-    const int row = qt * QM + tid;                        // my query row (TMEM lane tid)
 
     // my run of prefix rows, in whole tiles
     const int tiles_total = (prefix + KN - 1) / KN, per = (tiles_total + pa.n_runs - 1) / pa.n_runs;
@@ -118,174 +120,201 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const int nt = t_hi - t_lo;
     const int p_lo = t_lo * KN, p_end = min(prefix, t_hi * KN);
 
-    const uint32_t bar_q = s_base + OFF_BAR, bar_kv = bar_q + 8 /* two */, bar_s = bar_q + 24, bar_o = bar_q + 32;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 64);
+    // barriers: Q, K[2], V[2] (TMA), S[2] (S product landed in its buffer), O (O += P V done),
+    // P (all 128 softmax threads are through with S(t) and have written P(t))
+    const uint32_t bar_q = s_base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_q + 24, bar_s = bar_q + 40,
+                   bar_o = bar_q + 56, bar_p = bar_q + 64;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 96);
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_kv, 1);
-        mbar_init(bar_kv + 8, 1);
+        mbar_init(bar_k, 1);
+        mbar_init(bar_k + 8, 1);
+        mbar_init(bar_v, 1);
+        mbar_init(bar_v + 8, 1);
         mbar_init(bar_s, 1);
+        mbar_init(bar_s + 8, 1);
         mbar_init(bar_o, 1);
+        mbar_init(bar_p, QM);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {                                      // 256 columns of tensor memory: S and O
+    if (warp == 4) {                                      // tensor memory: two S buffers and O (384 of 512 columns)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     umma::fence_before_sync();
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;  // this warp's 32 TMEM lanes
+    const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;   // S(t) lives at tmem_s0 + (t & 1) * 128
 
-    auto load_kv = [&](int t, int st) {                   // thread 0: K and V tile t of my run
-        const uint32_t bar = bar_kv + st * 8;
-        mbar_arrive_expect_tx(bar, 2 * TILE);
+    if (warp == 4) {
+        // =============================== control: TMA and MMA issue ===============================
+        if ((tid & 31) == 0 && nt > 0) {
+            bool alive = true;
+            auto load_k = [&](int t) {
+                const uint32_t bar = bar_k + (t & 1) * 8;
+                mbar_arrive_expect_tx(bar, TILE);
+                tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, h, z, bar);
+                tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, h, z, bar);
+            };
+            auto load_v = [&](int t) {
+                const uint32_t bar = bar_v + (t & 1) * 8;
+                mbar_arrive_expect_tx(bar, TILE);
+                tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, h, z, bar);
+                tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, h, z, bar);
+            };
+            const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
+            auto issue_s = [&](int t) {                   // S(t) = Q K(t)^T into S buffer t & 1
+                const int st = t & 1;
+                alive = mbar_wait(bar_k + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                if (!alive) return;
+                umma::fence_after_sync();
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            tma_load_4d(s_base + OFF_K + st * TILE + hf * HALF, &tm_k, hf * 64, p_lo + t * KN, h, z, bar);
-            tma_load_4d(s_base + OFF_V + st * TILE + hf * HALF, &tm_v, hf * 64, p_lo + t * KN, h, z, bar);
-        }
-    };
-    if (tid == 0 && nt > 0) {
-        mbar_arrive_expect_tx(bar_q, TILE);
-        tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
-        tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
-        load_kv(0, 0);
-        if (nt > 1) load_kv(1, 1);
-    }
-
-    const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
-    const float c2 = a.scale_log2;
-    float m_ref = -INFINITY, l = 0.f;                     // reference point of the exponent, row sum
-    bool alive = true;
-
-    auto issue_s = [&](int t) {                           // thread 0: S = Q K^T for tile t
-        const int st = t & 1;
-        if (t == 0) alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
-        alive = mbar_wait(bar_kv + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-        if (!alive) return;
-        umma::fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t koff = (ks >> 2) * HALF + (ks & 3) * 32;
-            mma_f16(tmem_s, smem_desc(s_base + OFF_Q + koff, 16), smem_desc(s_base + OFF_K + st * TILE + koff, 16),
-                    idesc_s, ks > 0);
-        }
-        mma_commit(bar_s);
-    };
-    if (tid == 0 && nt > 0) issue_s(0);
-
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t koff = (ks >> 2) * HALF + (ks & 3) * 32;
+                    mma_f16(tmem_s0 + st * 128, smem_desc(s_base + OFF_Q + koff, 16),
+                            smem_desc(s_base + OFF_K + st * TILE + koff, 16), idesc_s, ks > 0);
+                }
+                mma_commit(bar_s + st * 8);
+            };
+            mbar_arrive_expect_tx(bar_q, TILE);
+            tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
+            tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
+            load_k(0);
+            if (nt > 1) load_k(1);
+            load_v(0);
+            if (nt > 1) load_v(1);
+            alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
+            issue_s(0);
 #pragma unroll 1
-    for (int t = 0; t < nt; ++t) {
-        const int st = t & 1;
-        alive = mbar_wait(bar_s, t & 1, a.status, qt) && alive;
-        // every thread must stay in step (the TMEM loads below are warp-wide), so a dead wait
-        // only poisons the result; thread 0 stops issuing
-        umma::fence_after_sync();
-        const int cols = min(KN, p_end - (p_lo + t * KN));       // valid columns of this tile
-
-        // ---- pass 1: row maximum
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c0 = 0; c0 < KN; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32(r, tmem_s + lane_base + c0);
+            for (int t = 0; t < nt && alive; ++t) {
+                const int st = t & 1;
+                // S(t+1) runs on the tensor core while the softmax warps work on S(t); its buffer
+                // was released when the softmax warps finished tile t-1
+                if (t + 1 < nt) issue_s(t + 1);
+                alive = mbar_wait(bar_p, t & 1, a.status, qt) && alive;          // P(t) is in shared memory
+                if (alive && t + 2 < nt) load_k(t + 2);                        // S(t) is done with K stage st
+                alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                if (!alive) break;
+                umma::fence_after_sync();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c0 + i < cols) ? __uint_as_float(r[i]) : -INFINITY);
-        }
-        // the reference point moves only when the maximum grows by more than 2^8
-        const bool up = (mx - m_ref) * c2 > 8.f;          // true from -inf
-        if (__any_sync(0xffffffffu, up) && t > 0) {       // rescale O in tensor memory (rare)
-            const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(r, tmem_o + lane_base + c0);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                tmem_st32(tmem_o + lane_base + c0, r);
+                for (int ks = 0; ks < KN / 16; ++ks) {    // O += P V, 16 prefix rows per step
+                    const uint32_t aoff = (ks >> 2) * HALF + (ks & 3) * 32;
+                    mma_f16(tmem_o, smem_desc(s_base + OFF_P + aoff, 16),
+                            smem_desc(s_base + OFF_V + st * TILE + ks * 16 * 128, HALF), idesc_pv, t > 0 || ks > 0);
+                }
+                mma_commit(bar_o);
+                if (t + 2 < nt) {                         // V stage st is free once that product has read it
+                    alive = mbar_wait(bar_o, t & 1, a.status, qt) && alive;
+                    if (alive) load_v(t + 2);
+                }
             }
-            l *= alpha;
         }
-        if (up) m_ref = mx;
-        const float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
-
-        // ---- pass 2: probabilities, row sum, P into shared memory (K-major, swizzled)
+    } else {
+        // =============================== softmax: one thread per query row ===============================
+        const int row = qt * QM + tid;                    // my query row (TMEM lane tid)
+        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        const float c2 = a.scale_log2;
+        float m_ref = -INFINITY, l = 0.f;                 // reference point of the exponent, row sum
+        bool alive = true;
         unsigned char *prow = smem + OFF_P + tid * 128;
 #pragma unroll 1
-        for (int c0 = 0; c0 < KN; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32(r, tmem_s + lane_base + c0);
-            uint32_t packed[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                const float p0 = (c0 + i < cols) ? fast_exp2(fmaf(__uint_as_float(r[i]), c2, -mu)) : 0.f;
-                const float p1 = (c0 + i + 1 < cols) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), c2, -mu)) : 0.f;
-                l += p0 + p1;
-                packed[i >> 1] = MT::pack(p0, p1);
-            }
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {              // four 16-byte chunks of my row
-                const int chunk = (c0 >> 3) + q4;         // 0..15 across the row
-                unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
-                *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2],
-                                                             packed[q4 * 4 + 3]);
-            }
-        }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P visible to the tensor core
-        umma::fence_before_sync();
-        __syncthreads();
-
-        if (tid == 0 && alive) {
+        for (int t = 0; t < nt; ++t) {
+            const int st = t & 1;
+            alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
             umma::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < KN / 16; ++ks) {        // O += P V, 16 prefix rows per step
-                const uint32_t aoff = (ks >> 2) * HALF + (ks & 3) * 32;
-                mma_f16(tmem_o, smem_desc(s_base + OFF_P + aoff, 16),
-                        smem_desc(s_base + OFF_V + st * TILE + ks * 16 * 128, HALF), idesc_pv, t > 0 || ks > 0);
-            }
-            mma_commit(bar_o);
-            if (t + 1 < nt) issue_s(t + 1);               // queued behind the product above
-            if (t + 2 < nt) {                             // stage st is free once O += P V has read it
-                alive = mbar_wait(bar_o, t & 1, a.status, qt) && alive;
-                if (alive) load_kv(t + 2, st);
-            }
-        }
-    }
+            const uint32_t tmem_s = tmem_s0 + st * 128;
+            const int cols = min(KN, p_end - (p_lo + t * KN));       // valid columns of this tile
+            const bool full = cols == KN;
 
-    // ---- epilogue: O / l and the log-sum-exp of my row into this run's partial-result slot
-    if (nt > 0) alive = mbar_wait(bar_o, (nt - 1) & 1, a.status, qt) && alive;
-    umma::fence_after_sync();
-    const size_t slot = size_t(pa.first_slot + run);
-    const size_t prow = ((slot * a.Z + z) * a.H + h) * n_q + row;
-    const float inv = (l > 0.f && alive) ? 1.f / l : 0.f;
+            // ---- pass 1: row maximum
+            float mx = -INFINITY;
 #pragma unroll 1
-    for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
-        if (nt > 0) {
-            tmem_ld32(r, tmem_o + lane_base + c0);
-        } else {
+            for (int c0 = 0; c0 < KN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(r, tmem_s + lane_base + c0);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        if (row < n_q) {
-            float4 *dst = reinterpret_cast<float4 *>(a.part_o + prow * D + c0);
+                for (int i = 0; i < 32; ++i)
+                    mx = fmaxf(mx, (full || c0 + i < cols) ? __uint_as_float(r[i]) : -INFINITY);
+            }
+            // O and the P buffer belong to the tensor core until O += P V of the tile before is done
+            if (t > 0) alive = mbar_wait(bar_o, (t - 1) & 1, a.status, qt) && alive;
+            umma::fence_after_sync();
+            // the reference point moves only when the maximum grows by more than 2^8
+            const bool up = (mx - m_ref) * c2 > 8.f;      // true from -inf
+            if (__any_sync(0xffffffffu, up) && t > 0) {   // rescale O in tensor memory (rare)
+                const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(r, tmem_o + lane_base + c0);
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-                dst[i >> 2] = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                          __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st32(tmem_o + lane_base + c0, r);
+                }
+                l *= alpha;
+            }
+            if (up) m_ref = mx;
+            const float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
+
+            // ---- pass 2: probabilities, row sum, P into shared memory (K-major, swizzled)
+#pragma unroll 1
+            for (int c0 = 0; c0 < KN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(r, tmem_s + lane_base + c0);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = (full || c0 + i < cols) ? fast_exp2(fmaf(__uint_as_float(r[i]), c2, -mu)) : 0.f;
+                    const float p1 = (full || c0 + i + 1 < cols) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), c2, -mu)) : 0.f;
+                    l += p0 + p1;
+                    packed[i >> 1] = MT::pack(p0, p1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {          // four 16-byte chunks of my row
+                    const int chunk = (c0 >> 3) + q4;     // 0..15 across the row
+                    unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1],
+                                                                 packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P visible to the tensor core
+            umma::fence_before_sync();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_p) : "memory");
         }
+
+        // ---- epilogue: O / l and the log-sum-exp of my row into this run's partial-result slot
+        if (nt > 0) alive = mbar_wait(bar_o, (nt - 1) & 1, a.status, qt) && alive;
+        umma::fence_after_sync();
+        const size_t slot = size_t(pa.first_slot + run);
+        const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + row;
+        const float inv = (l > 0.f && alive) ? 1.f / l : 0.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t r[32];
+            if (nt > 0) {
+                tmem_ld32(r, tmem_o + lane_base + c0);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (row < n_q) {
+                float4 *dst = reinterpret_cast<float4 *>(a.part_o + prow_g * D + c0);
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    dst[i >> 2] = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                              __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            }
+        }
+        if (row < n_q) a.part_lse[prow_g] = (l > 0.f && alive) ? m_ref * c2 + log2f(l) : -INFINITY;
     }
-    if (row < n_q) a.part_lse[prow] = (l > 0.f && alive) ? m_ref * c2 + log2f(l) : -INFINITY;
 
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256) : "memory");
+    if (warp == 4)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
 // rank-4 map with 64-column x 128-row boxes
@@ -323,7 +352,7 @@ static cudaError_t launch_prefix_t(const AttnArgs &a, int n_runs, int first_slot
     if ((long long)a.Z * n_runs > 65535) return cudaErrorInvalidValue;
     PrefixArgs pa{n_runs, first_slot};
     dim3 grid((a.n_q + umma::QM - 1) / umma::QM, a.H, a.Z * n_runs);
-    prefix_umma_kernel<T><<<grid, 128, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
+    prefix_umma_kernel<T><<<grid, PFX_THREADS, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
     return cudaGetLastError();
 }
 
