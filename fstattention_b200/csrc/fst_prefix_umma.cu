@@ -31,7 +31,7 @@ constexpr int HALF = QM * 128;         // bytes of one 64-column half of a 128-r
 constexpr int TILE = 2 * HALF;         // bytes of a 128 x 128 fp16 tile
 constexpr int OFF_Q = 0;
 constexpr int OFF_P = OFF_Q + TILE;
-constexpr int OFF_K = OFF_P + TILE;    // two stages
+constexpr int OFF_K = OFF_P + 2 * TILE;    // P is double buffered; K and V have two stages each
 constexpr int OFF_V = OFF_K + 2 * TILE;
 constexpr int OFF_BAR = OFF_V + 2 * TILE;
 constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;   // + barriers, TMEM address, 1 KB alignment slack
@@ -63,6 +63,7 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
+// asynchronous: the registers are valid after tmem_ld_wait()
 __device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32"
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
@@ -72,7 +73,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+// The loaded registers pass through the wait as read-write operands, so that no use of them can
+// be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
@@ -120,11 +130,12 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const int nt = t_hi - t_lo;
     const int p_lo = t_lo * KN, p_end = min(prefix, t_hi * KN);
 
-    // barriers: Q, K[2], V[2] (TMA), S[2] (S product landed in its buffer), O (O += P V done),
-    // P (all 128 softmax threads are through with S(t) and have written P(t))
+    // barriers: Q, K[2], V[2] (TMA), S[2] (S product landed in its buffer), O[2] (O += P V done, per P buffer),
+    // P[2] (all 128 softmax threads are through with S(t) and have written P(t)).  Every barrier that is
+    // indexed by t & 1 completes once per two tiles, so a waiter can never fall two phases behind.
     const uint32_t bar_q = s_base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_q + 24, bar_s = bar_q + 40,
-                   bar_o = bar_q + 56, bar_p = bar_q + 64;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 96);
+                   bar_o = bar_q + 56 /* two: one per P buffer */, bar_p = bar_q + 72;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 112);
 
     if (tid == 0) {
         mbar_init(bar_q, 1);
@@ -135,7 +146,9 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         mbar_init(bar_s, 1);
         mbar_init(bar_s + 8, 1);
         mbar_init(bar_o, 1);
+        mbar_init(bar_o + 8, 1);
         mbar_init(bar_p, QM);
+        mbar_init(bar_p + 8, QM);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 4) {                                      // tensor memory: two S buffers and O (384 of 512 columns)
@@ -194,20 +207,23 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
                 // S(t+1) runs on the tensor core while the softmax warps work on S(t); its buffer
                 // was released when the softmax warps finished tile t-1
                 if (t + 1 < nt) issue_s(t + 1);
-                alive = mbar_wait(bar_p, t & 1, a.status, qt) && alive;          // P(t) is in shared memory
-                if (alive && t + 2 < nt) load_k(t + 2);                        // S(t) is done with K stage st
+                if (alive && t + 2 < nt) {                // K stage st is free as soon as S(t) has been formed
+                    alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                    if (alive) load_k(t + 2);
+                }
+                alive = mbar_wait(bar_p + st * 8, (t >> 1) & 1, a.status, qt) && alive;   // P(t) is in shared memory
                 alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
                 if (!alive) break;
                 umma::fence_after_sync();
 #pragma unroll
                 for (int ks = 0; ks < KN / 16; ++ks) {    // O += P V, 16 prefix rows per step
                     const uint32_t aoff = (ks >> 2) * HALF + (ks & 3) * 32;
-                    mma_f16(tmem_o, smem_desc(s_base + OFF_P + aoff, 16),
+                    mma_f16(tmem_o, smem_desc(s_base + OFF_P + st * TILE + aoff, 16),
                             smem_desc(s_base + OFF_V + st * TILE + ks * 16 * 128, HALF), idesc_pv, t > 0 || ks > 0);
                 }
-                mma_commit(bar_o);
+                mma_commit(bar_o + st * 8);
                 if (t + 2 < nt) {                         // V stage st is free once that product has read it
-                    alive = mbar_wait(bar_o, t & 1, a.status, qt) && alive;
+                    alive = mbar_wait(bar_o + st * 8, (t >> 1) & 1, a.status, qt) && alive;
                     if (alive) load_v(t + 2);
                 }
             }
@@ -219,74 +235,95 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         const float c2 = a.scale_log2;
         float m_ref = -INFINITY, l = 0.f;                 // reference point of the exponent, row sum
         bool alive = true;
-        unsigned char *prow = smem + OFF_P + tid * 128;
 #pragma unroll 1
         for (int t = 0; t < nt; ++t) {
             const int st = t & 1;
             alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
             umma::fence_after_sync();
             const uint32_t tmem_s = tmem_s0 + st * 128;
+            unsigned char *prow = smem + OFF_P + st * TILE + tid * 128;   // my row of P buffer st
             const int cols = min(KN, p_end - (p_lo + t * KN));       // valid columns of this tile
             const bool full = cols == KN;
 
-            // ---- pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(r, tmem_s + lane_base + c0);
+            // One pass over S when possible: probabilities are formed against the current
+            // reference point while the row maximum is tracked; only if some row's maximum has
+            // outgrown the reference by more than 2^8 (always on the first tile) is the reference
+            // moved, O rescaled, and the tile redone.  S is read 32 columns at a time, the next
+            // load in flight while the current one is processed.
+            float mx = -INFINITY, l_tile = 0.f;           // results of a sweep
+            float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
+            auto sweep = [&](bool write_p) {
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t ra[32], rb[32];
+                tmem_ld32(ra, tmem_s + lane_base);
+                tmem_ld_wait(ra);
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    mx = fmaxf(mx, (full || c0 + i < cols) ? __uint_as_float(r[i]) : -INFINITY);
-            }
-            // O and the P buffer belong to the tensor core until O += P V of the tile before is done
-            if (t > 0) alive = mbar_wait(bar_o, (t - 1) & 1, a.status, qt) && alive;
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t (&cur)[32] = (c & 1) ? rb : ra;
+                    uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
+                    if (c < 3) tmem_ld32(nxt, tmem_s + lane_base + (c + 1) * 32);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float s0 = __uint_as_float(cur[i]), s1 = __uint_as_float(cur[i + 1]);
+                        if (!full) {
+                            if (c * 32 + i >= cols) s0 = -INFINITY;
+                            if (c * 32 + i + 1 >= cols) s1 = -INFINITY;
+                        }
+                        mx4[(i >> 1) & 3] = fmaxf(mx4[(i >> 1) & 3], fmaxf(s0, s1));   // four independent chains
+                        if (write_p) {
+                            const float p0 = fast_exp2(fmaf(s0, c2, -mu)), p1 = fast_exp2(fmaf(s1, c2, -mu));
+                            l4[(i >> 1) & 3] += p0 + p1;
+                            packed[i >> 1] = MT::pack(p0, p1);
+                        }
+                    }
+                    if (write_p) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of my row, swizzled
+                            const int chunk = c * 4 + q4;
+                            unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
+                            *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1],
+                                                                         packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                        }
+                    }
+                    if (c < 3) tmem_ld_wait(nxt);
+                }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                l_tile = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            };
+            // P buffer st belongs to the tensor core until O += P V of tile t-2 is done
+            if (t > 1) alive = mbar_wait(bar_o + st * 8, ((t >> 1) - 1) & 1, a.status, qt) && alive;
             umma::fence_after_sync();
-            // the reference point moves only when the maximum grows by more than 2^8
+            sweep(t > 0);                                 // first tile: maximum only
             const bool up = (mx - m_ref) * c2 > 8.f;      // true from -inf
-            if (__any_sync(0xffffffffu, up) && t > 0) {   // rescale O in tensor memory (rare)
-                const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
+            if (__any_sync(0xffffffffu, up) || t == 0) {  // move the reference point (rare after tile 0)
+                if (t > 0) {                              // rescale O in tensor memory, once nothing is adding to it
+                    alive = mbar_wait(bar_o + (st ^ 1) * 8, ((t - 1) >> 1) & 1, a.status, qt) && alive;
+                    umma::fence_after_sync();
+                    const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(r, tmem_o + lane_base + c0);
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(r, tmem_o + lane_base + c0);
+                        tmem_ld_wait(r);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    tmem_st32(tmem_o + lane_base + c0, r);
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st32(tmem_o + lane_base + c0, r);
+                    }
+                    l *= alpha;
                 }
-                l *= alpha;
+                if (up) m_ref = mx;
+                mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
+                sweep(true);
             }
-            if (up) m_ref = mx;
-            const float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
-
-            // ---- pass 2: probabilities, row sum, P into shared memory (K-major, swizzled)
-#pragma unroll 1
-            for (int c0 = 0; c0 < KN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(r, tmem_s + lane_base + c0);
-                uint32_t packed[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = (full || c0 + i < cols) ? fast_exp2(fmaf(__uint_as_float(r[i]), c2, -mu)) : 0.f;
-                    const float p1 = (full || c0 + i + 1 < cols) ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), c2, -mu)) : 0.f;
-                    l += p0 + p1;
-                    packed[i >> 1] = MT::pack(p0, p1);
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {          // four 16-byte chunks of my row
-                    const int chunk = (c0 >> 3) + q4;     // 0..15 across the row
-                    unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
-                    *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1],
-                                                                 packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-                }
-            }
+            l += l_tile;
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P visible to the tensor core
             umma::fence_before_sync();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_p) : "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_p + st * 8) : "memory");
         }
 
         // ---- epilogue: O / l and the log-sum-exp of my row into this run's partial-result slot
-        if (nt > 0) alive = mbar_wait(bar_o, (nt - 1) & 1, a.status, qt) && alive;
+        if (nt > 0) alive = mbar_wait(bar_o + ((nt - 1) & 1) * 8, ((nt - 1) >> 1) & 1, a.status, qt) && alive;
         umma::fence_after_sync();
         const size_t slot = size_t(pa.first_slot + run);
         const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + row;
@@ -296,6 +333,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
             uint32_t r[32];
             if (nt > 0) {
                 tmem_ld32(r, tmem_o + lane_base + c0);
+                tmem_ld_wait(r);
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) r[i] = 0u;

@@ -50,7 +50,8 @@ def _pick_splits(kv_splits, q, prefix, block_m, kernel):
 
     Only the tensor-core kernels split.  With head_dim 128 and at least 256 prefix rows the
     prefix goes to the tcgen05 kernel (one CTA per 128 query rows, head, batch element and run;
-    the automatic choice aims at two CTAs per SM, runs of at least 256 rows); otherwise the tree
+    the automatic choice aims at one CTA per SM, which is all its shared memory allows, in runs of at
+    least 256 rows); otherwise the tree
     kernel walks the prefix itself, split to about four CTAs per SM."""
     if q.dtype not in (torch.float16, torch.bfloat16) or q.shape[-1] not in (64, 128) \
             or block_m not in (32, 64, 128) or kernel in ("simt", "mma") or prefix <= 0:
@@ -64,7 +65,7 @@ def _pick_splits(kv_splits, q, prefix, block_m, kernel):
         if kv_splits is not None:
             return max(1, min(int(kv_splits), z_cap)), True
         ctas = q.shape[0] * q.shape[1] * -(-q.shape[2] // 128)
-        return int(max(1, min((2 * sms) // max(ctas, 1), prefix // 256, z_cap))), True
+        return int(max(1, min(sms // max(ctas, 1), prefix // 256, z_cap))), True
     if kv_splits is not None:
         splits = max(1, min(int(kv_splits), z_cap))
         return splits, splits > 1
