@@ -36,6 +36,39 @@ static bool mma_ok(int dtype, int D, int bm) {
            (bm == 16 || bm == 32 || bm == 64 || bm == 128);
 }
 
+// A second stream with a fork and a join event, per host thread and device, so that two
+// independent kernels of one call can run side by side.  Created on first use and kept for the
+// life of the thread; never created while the caller's stream is being captured into a graph
+// (the call then simply runs its kernels in order).
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static SideStream *side_stream(cudaStream_t caller) {
+    thread_local SideStream per_device[kMaxDevices];
+    const int slot = current_device_slot();
+    if (slot < 0) return nullptr;
+    SideStream &s = per_device[slot];
+    if (s.stream != nullptr) return &s;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(caller, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    SideStream made;
+    if (cudaStreamCreateWithFlags(&made.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&made.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&made.join, cudaEventDisableTiming) != cudaSuccess) {
+        if (made.join != nullptr) cudaEventDestroy(made.join);
+        if (made.fork != nullptr) cudaEventDestroy(made.fork);
+        if (made.stream != nullptr) cudaStreamDestroy(made.stream);
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    s = made;
+    return &s;
+}
+
 static int cuda_status(cudaError_t e) {
     if (e == cudaSuccess) return FST_OK;
     if (e == cudaErrorNotSupported) return FST_ERR_UNSUPPORTED;
@@ -205,9 +238,24 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
         a.part_lse = a.part_o + size_t(a.part_slots) * Z * H * n_q * head_dim;
         cudaError_t e;
         if (want_umma) {
+            // The tree kernel (slot 0) and the prefix kernel (slots 1..) are independent: the tree
+            // kernel runs on a second stream, forked from and joined back into the caller's.  The
+            // prefix kernel is launched first: its CTAs need a whole SM's shared memory each and
+            // would otherwise queue behind the tree kernel's, which fit beside one another.
             a.skip_prefix = 1;
-            e = launch_attention_mma(a, dtype, FST_KERNEL_TMA, st);
-            if (e == cudaSuccess) e = launch_prefix_umma(a, dtype, kv_splits, 1, st);
+            SideStream *side = side_stream(st);
+            cudaStream_t tree_st = st;
+            if (side != nullptr && cudaEventRecord(side->fork, st) == cudaSuccess &&
+                cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+                tree_st = side->stream;
+            e = launch_prefix_umma(a, dtype, kv_splits, 1, st);
+            const cudaError_t et = launch_attention_mma(a, dtype, FST_KERNEL_TMA, tree_st);
+            if (tree_st != st) {                          // always join what was forked
+                cudaError_t ej = cudaEventRecord(side->join, tree_st);
+                if (ej == cudaSuccess) ej = cudaStreamWaitEvent(st, side->join, 0);
+                if (e == cudaSuccess) e = ej;
+            }
+            if (e == cudaSuccess) e = et;
         } else {
             a.n_splits = kv_splits;
             e = launch_attention_mma(a, dtype, choice, st);

@@ -493,18 +493,37 @@ combine_splits_kernel(const AttnArgs a) {
     const size_t row = idx / CPR;
     const int c = int(idx - row * CPR) * 4;
     if (row >= rows) return;
+    // Loads go out four slots at a time so that their latencies overlap.
+    constexpr int U = 4;
     float big = -INFINITY;
-    for (int s = 0; s < a.part_slots; ++s) big = fmaxf(big, a.part_lse[size_t(s) * rows + row]);
+    for (int s0 = 0; s0 < a.part_slots; s0 += U) {
+        float ls[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            ls[u] = s0 + u < a.part_slots ? a.part_lse[size_t(s0 + u) * rows + row] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < U; ++u) big = fmaxf(big, ls[u]);
+    }
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    for (int s = 0; s < a.part_slots; ++s) {
-        const float ls = a.part_lse[size_t(s) * rows + row];
-        if (ls == -INFINITY) continue;
-        const float w = exp2f(ls - big);
-        const float4 v = *reinterpret_cast<const float4 *>(a.part_o + (size_t(s) * rows + row) * D + c);
-        sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y);
-        sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
-        wsum += w;
+    for (int s0 = 0; s0 < a.part_slots; s0 += U) {
+        float ls[U];
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const bool in = s0 + u < a.part_slots;
+            ls[u] = in ? a.part_lse[size_t(s0 + u) * rows + row] : -INFINITY;
+            v[u] = in ? *reinterpret_cast<const float4 *>(a.part_o + (size_t(s0 + u) * rows + row) * D + c)
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (ls[u] == -INFINITY) continue;            // an empty run: its O row is not meaningful
+            const float w = exp2f(ls[u] - big);
+            sum.x = fmaf(w, v[u].x, sum.x); sum.y = fmaf(w, v[u].y, sum.y);
+            sum.z = fmaf(w, v[u].z, sum.z); sum.w = fmaf(w, v[u].w, sum.w);
+            wsum += w;
+        }
     }
     const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
     const size_t n = row % a.n_q, zh = row / a.n_q;

@@ -106,7 +106,8 @@ struct PrefixArgs {
     int first_slot;      // partial-result slot of run 0 (slot 0 belongs to the tree kernel)
 };
 
-constexpr int PFX_THREADS = 160;       // four softmax warps (one thread per query row) + one control warp
+constexpr int PFX_SOFTMAX = 256;       // eight softmax warps: two groups of 128, one thread per query row each
+constexpr int PFX_THREADS = PFX_SOFTMAX + 64;   // + two issuing warps
 
 template <typename T>
 __global__ void __launch_bounds__(PFX_THREADS, 1)
@@ -131,27 +132,49 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const int p_lo = t_lo * KN, p_end = min(prefix, t_hi * KN);
 
     // barriers: Q, K[2], V[2] (TMA), S[2] (S product landed in its buffer), O[2] (O += P V done, per P buffer),
-    // P[2] (all 128 softmax threads are through with S(t) and have written P(t)).  Every barrier that is
+    // P[2] (all softmax threads are through with S(t) and have written P(t)).  Every barrier that is
     // indexed by t & 1 completes once per two tiles, so a waiter can never fall two phases behind.
     const uint32_t bar_q = s_base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_q + 24, bar_s = bar_q + 40,
-                   bar_o = bar_q + 56 /* two: one per P buffer */, bar_p = bar_q + 72;
+                   bar_o = bar_q + 56, bar_p = bar_q + 72;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 112);
 
-    if (tid == 0) {
+    // Thread 256 sets the barriers up and sends the first loads off before the CTA-wide sync, so
+    // that they are under way while warp 9 allocates tensor memory.
+    auto load_k = [&](int t) {
+        const uint32_t bar = bar_k + (t & 1) * 8;
+        mbar_arrive_expect_tx(bar, TILE);
+        tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, h, z, bar);
+        tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, h, z, bar);
+    };
+    auto load_v = [&](int t) {
+        const uint32_t bar = bar_v + (t & 1) * 8;
+        mbar_arrive_expect_tx(bar, TILE);
+        tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, h, z, bar);
+        tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, h, z, bar);
+    };
+    if (tid == PFX_SOFTMAX) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_k, 1);
-        mbar_init(bar_k + 8, 1);
-        mbar_init(bar_v, 1);
-        mbar_init(bar_v + 8, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_s + 8, 1);
-        mbar_init(bar_o, 1);
-        mbar_init(bar_o + 8, 1);
-        mbar_init(bar_p, QM);
-        mbar_init(bar_p + 8, QM);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_k + i * 8, 1);
+            mbar_init(bar_v + i * 8, 1);
+            mbar_init(bar_s + i * 8, 1);
+            mbar_init(bar_o + i * 8, 1);
+            mbar_init(bar_p + i * 8, PFX_SOFTMAX / 2);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        if (nt > 0) {
+            mbar_arrive_expect_tx(bar_q, TILE);
+            tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
+            tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
+            load_k(0);
+            load_v(0);
+            if (nt > 1) {
+                load_k(1);
+                load_v(1);
+            }
+        }
     }
-    if (warp == 4) {                                      // tensor memory: two S buffers and O (384 of 512 columns)
+    if (warp == 9) {                                      // tensor memory: two S buffers and two accumulators, 128 columns each
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -160,66 +183,50 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;   // S(t) lives at tmem_s0 + (t & 1) * 128
+    const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;   // S(t) at tmem_s0 + (t & 1) * 128, O_g at tmem_o + g * 128
 
-    if (warp == 4) {
-        // =============================== control: TMA and MMA issue ===============================
-        if ((tid & 31) == 0 && nt > 0) {
-            bool alive = true;
-            auto load_k = [&](int t) {
-                const uint32_t bar = bar_k + (t & 1) * 8;
-                mbar_arrive_expect_tx(bar, TILE);
-                tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, h, z, bar);
-                tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, h, z, bar);
-            };
-            auto load_v = [&](int t) {
-                const uint32_t bar = bar_v + (t & 1) * 8;
-                mbar_arrive_expect_tx(bar, TILE);
-                tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, h, z, bar);
-                tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, h, z, bar);
-            };
-            const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
-            auto issue_s = [&](int t) {                   // S(t) = Q K(t)^T into S buffer t & 1
+    if (warp >= 8) {
+        // ================ two issuing threads: warp 8 for K and S = Q K^T, warp 9 for V and O += P V ================
+        const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
+        bool alive = true;
+        if (tid == PFX_SOFTMAX && nt > 0) {
+            // descriptors of the tiles' first 16-wide step; a step further on adds its byte offset / 16
+            const uint64_t dq = smem_desc(s_base + OFF_Q, 16), dk = smem_desc(s_base + OFF_K, 16);
+            alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
+#pragma unroll 1
+            for (int t = 0; t < nt && alive; ++t) {       // S(t) = Q K(t)^T into S buffer t & 1
                 const int st = t & 1;
+                // the buffer is free when the softmax warps are through with tile t-2
+                if (t > 1) alive = mbar_wait(bar_p + st * 8, ((t >> 1) - 1) & 1, a.status, qt) && alive;
                 alive = mbar_wait(bar_k + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                if (!alive) return;
+                if (!alive) break;
                 umma::fence_after_sync();
+                const uint64_t dks = dk + uint64_t(st * (TILE >> 4));
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t koff = (ks >> 2) * HALF + (ks & 3) * 32;
-                    mma_f16(tmem_s0 + st * 128, smem_desc(s_base + OFF_Q + koff, 16),
-                            smem_desc(s_base + OFF_K + st * TILE + koff, 16), idesc_s, ks > 0);
+                    const uint64_t koff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
+                    mma_f16(tmem_s0 + st * 128, dq + koff, dks + koff, idesc_s, ks > 0);
                 }
                 mma_commit(bar_s + st * 8);
-            };
-            mbar_arrive_expect_tx(bar_q, TILE);
-            tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
-            tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
-            load_k(0);
-            if (nt > 1) load_k(1);
-            load_v(0);
-            if (nt > 1) load_v(1);
-            alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
-            issue_s(0);
-#pragma unroll 1
-            for (int t = 0; t < nt && alive; ++t) {
-                const int st = t & 1;
-                // S(t+1) runs on the tensor core while the softmax warps work on S(t); its buffer
-                // was released when the softmax warps finished tile t-1
-                if (t + 1 < nt) issue_s(t + 1);
-                if (alive && t + 2 < nt) {                // K stage st is free as soon as S(t) has been formed
+                if (t + 2 < nt) {                         // K stage st is free as soon as S(t) has been formed
                     alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
                     if (alive) load_k(t + 2);
                 }
+            }
+        } else if (tid == PFX_SOFTMAX + 32 && nt > 0) {
+            const uint64_t dp = smem_desc(s_base + OFF_P, 16), dv = smem_desc(s_base + OFF_V, HALF);
+#pragma unroll 1
+            for (int t = 0; t < nt && alive; ++t) {       // O_g += P(t) V(t), g = t & 1
+                const int st = t & 1;
                 alive = mbar_wait(bar_p + st * 8, (t >> 1) & 1, a.status, qt) && alive;   // P(t) is in shared memory
                 alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
                 if (!alive) break;
                 umma::fence_after_sync();
+                const uint64_t dps = dp + uint64_t(st * (TILE >> 4)), dvs = dv + uint64_t(st * (TILE >> 4));
 #pragma unroll
-                for (int ks = 0; ks < KN / 16; ++ks) {    // O += P V, 16 prefix rows per step
-                    const uint32_t aoff = (ks >> 2) * HALF + (ks & 3) * 32;
-                    mma_f16(tmem_o, smem_desc(s_base + OFF_P + st * TILE + aoff, 16),
-                            smem_desc(s_base + OFF_V + st * TILE + ks * 16 * 128, HALF), idesc_pv, t > 0 || ks > 0);
+                for (int ks = 0; ks < KN / 16; ++ks) {    // 16 prefix rows per step
+                    const uint64_t aoff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
+                    mma_f16(tmem_o + st * 128, dps + aoff, dvs + uint64_t((ks * 16 * 128) >> 4), idesc_pv, t > 1 || ks > 0);
                 }
                 mma_commit(bar_o + st * 8);
                 if (t + 2 < nt) {                         // V stage st is free once that product has read it
@@ -229,129 +236,168 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
             }
         }
     } else {
-        // =============================== softmax: one thread per query row ===============================
-        const int row = qt * QM + tid;                    // my query row (TMEM lane tid)
-        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        // ============ softmax: two groups of 128 threads, one thread per query row, alternating tiles ============
+        // Group g owns the tiles with t & 1 == g: S buffer g, P buffer g and the accumulator O_g,
+        // with its own reference point and row sum, so the groups never wait for one another and
+        // one group's waits and tensor-memory latencies hide behind the other's exponentials.
+        const int r = tid & 127, g = tid >> 7;            // my query row (TMEM lane r) and group
+        const int row = qt * QM + r;
+        const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+        const uint32_t tmem_s = tmem_s0 + g * 128, tmem_og = tmem_o + g * 128;
+        unsigned char *prow = smem + OFF_P + g * TILE + r * 128;   // my row of P buffer g
         const float c2 = a.scale_log2;
         float m_ref = -INFINITY, l = 0.f;                 // reference point of the exponent, row sum
         bool alive = true;
+        float mx = -INFINITY, l_tile = 0.f, mu = 0.f;     // results / parameter of a sweep
+
+        // One sweep over my row of S: row maximum, and (WRITE) probabilities against the reference
+        // point into my row of P plus their sum.  MASK: columns >= cols are -inf.  S is read 32
+        // columns at a time, the next load in flight while the current one is processed.
+        auto sweep = [&](auto write_c, auto mask_c, int cols) {
+            constexpr bool WRITE = decltype(write_c)::value, MASK = decltype(mask_c)::value;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t ra[32], rb[32];
+            tmem_ld32(ra, tmem_s + lane_base);
+            tmem_ld_wait(ra);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t (&cur)[32] = (c & 1) ? rb : ra;
+                uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
+                if (c < 3) tmem_ld32(nxt, tmem_s + lane_base + (c + 1) * 32);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float s0 = __uint_as_float(cur[i]), s1 = __uint_as_float(cur[i + 1]);
+                    if (MASK) {
+                        if (c * 32 + i >= cols) s0 = -INFINITY;
+                        if (c * 32 + i + 1 >= cols) s1 = -INFINITY;
+                    }
+                    mx4[(i >> 1) & 3] = fmaxf(mx4[(i >> 1) & 3], fmaxf(s0, s1));   // four independent chains
+                    if (WRITE) {
+                        const float p0 = fast_exp2(fmaf(s0, c2, -mu)), p1 = fast_exp2(fmaf(s1, c2, -mu));
+                        l4[(i >> 1) & 3] += p0 + p1;
+                        packed[i >> 1] = MT::pack(p0, p1);
+                    }
+                }
+                if (WRITE) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {      // four 16-byte chunks of my row, swizzled
+                        const int chunk = c * 4 + q4;
+                        *reinterpret_cast<uint4 *>(prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (r & 7)) << 4)) =
+                            make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                    }
+                }
+                if (c < 3) tmem_ld_wait(nxt);
+            }
+            mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            l_tile = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        };
+        const std::true_type yes{};
+        const std::false_type no{};
+
+        int n_mine = 0;                                   // tiles my group has taken
 #pragma unroll 1
-        for (int t = 0; t < nt; ++t) {
-            const int st = t & 1;
-            alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+        for (int t = g; t < nt; t += 2, ++n_mine) {
+            alive = mbar_wait(bar_s + g * 8, n_mine & 1, a.status, qt) && alive;
+            // P buffer g and O_g belong to the tensor core until O_g += P V of my previous tile is done
+            if (n_mine > 0) alive = mbar_wait(bar_o + g * 8, (n_mine - 1) & 1, a.status, qt) && alive;
             umma::fence_after_sync();
-            const uint32_t tmem_s = tmem_s0 + st * 128;
-            unsigned char *prow = smem + OFF_P + st * TILE + tid * 128;   // my row of P buffer st
             const int cols = min(KN, p_end - (p_lo + t * KN));       // valid columns of this tile
             const bool full = cols == KN;
 
-            // One pass over S when possible: probabilities are formed against the current
-            // reference point while the row maximum is tracked; only if some row's maximum has
-            // outgrown the reference by more than 2^8 (always on the first tile) is the reference
-            // moved, O rescaled, and the tile redone.  S is read 32 columns at a time, the next
-            // load in flight while the current one is processed.
-            float mx = -INFINITY, l_tile = 0.f;           // results of a sweep
-            float mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
-            auto sweep = [&](bool write_p) {
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t ra[32], rb[32];
-                tmem_ld32(ra, tmem_s + lane_base);
-                tmem_ld_wait(ra);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t (&cur)[32] = (c & 1) ? rb : ra;
-                    uint32_t (&nxt)[32] = (c & 1) ? ra : rb;
-                    if (c < 3) tmem_ld32(nxt, tmem_s + lane_base + (c + 1) * 32);
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(cur[i]), s1 = __uint_as_float(cur[i + 1]);
-                        if (!full) {
-                            if (c * 32 + i >= cols) s0 = -INFINITY;
-                            if (c * 32 + i + 1 >= cols) s1 = -INFINITY;
-                        }
-                        mx4[(i >> 1) & 3] = fmaxf(mx4[(i >> 1) & 3], fmaxf(s0, s1));   // four independent chains
-                        if (write_p) {
-                            const float p0 = fast_exp2(fmaf(s0, c2, -mu)), p1 = fast_exp2(fmaf(s1, c2, -mu));
-                            l4[(i >> 1) & 3] += p0 + p1;
-                            packed[i >> 1] = MT::pack(p0, p1);
-                        }
-                    }
-                    if (write_p) {
-#pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of my row, swizzled
-                            const int chunk = c * 4 + q4;
-                            unsigned char *dst = prow + (chunk >> 3) * HALF + (((chunk & 7) ^ (tid & 7)) << 4);
-                            *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1],
-                                                                         packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
-                        }
-                    }
-                    if (c < 3) tmem_ld_wait(nxt);
-                }
-                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                l_tile = (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            };
-            // P buffer st belongs to the tensor core until O += P V of tile t-2 is done
-            if (t > 1) alive = mbar_wait(bar_o + st * 8, ((t >> 1) - 1) & 1, a.status, qt) && alive;
-            umma::fence_after_sync();
-            sweep(t > 0);                                 // first tile: maximum only
-            const bool up = (mx - m_ref) * c2 > 8.f;      // true from -inf
-            if (__any_sync(0xffffffffu, up) || t == 0) {  // move the reference point (rare after tile 0)
-                if (t > 0) {                              // rescale O in tensor memory, once nothing is adding to it
-                    alive = mbar_wait(bar_o + (st ^ 1) * 8, ((t - 1) >> 1) & 1, a.status, qt) && alive;
-                    umma::fence_after_sync();
-                    const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
+            // Probabilities are formed against the current reference point while the row maximum
+            // is tracked (one pass over S).  Only if a row of my warp has outgrown its reference
+            // by more than 2^8 (always on the first tile) is the reference moved, O_g rescaled,
+            // and the tile done again.
+            if (n_mine == 0) sweep(no, yes, cols);        // maximum only
 #pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        uint32_t r[32];
-                        tmem_ld32(r, tmem_o + lane_base + c0);
-                        tmem_ld_wait(r);
+            for (int pass = 0; pass < 2; ++pass) {
+                if (pass == 1 || n_mine == 0) {
+                    const bool up = (mx - m_ref) * c2 > 8.f;          // true from -inf
+                    if (n_mine > 0) {                     // rescale my row of O_g in tensor memory
+                        const float alpha = up ? fast_exp2((m_ref - mx) * c2) : 1.f;
+#pragma unroll 1
+                        for (int c0 = 0; c0 < D; c0 += 32) {
+                            uint32_t o[32];
+                            tmem_ld32(o, tmem_og + lane_base + c0);
+                            tmem_ld_wait(o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(tmem_o + lane_base + c0, r);
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tmem_og + lane_base + c0, o);
+                        }
+                        l *= alpha;
                     }
-                    l *= alpha;
+                    if (up) m_ref = mx;
+                    mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
                 }
-                if (up) m_ref = mx;
-                mu = m_ref == -INFINITY ? 0.f : m_ref * c2;
-                sweep(true);
+                if (full) sweep(yes, no, cols);
+                else sweep(yes, yes, cols);
+                if (!__any_sync(0xffffffffu, (mx - m_ref) * c2 > 8.f)) break;
             }
             l += l_tile;
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P visible to the tensor core
             umma::fence_before_sync();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_p + st * 8) : "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_p + g * 8) : "memory");
         }
 
-        // ---- epilogue: O / l and the log-sum-exp of my row into this run's partial-result slot
-        if (nt > 0) alive = mbar_wait(bar_o + ((nt - 1) & 1) * 8, ((nt - 1) >> 1) & 1, a.status, qt) && alive;
+        // ---- epilogue: merge the two groups' results; O / l and the log-sum-exp of every row go to
+        // this run's partial-result slot.  Each thread puts its unnormalised row of O_g into shared
+        // memory (the K and V stages, free once every product is done; the (exponent, sum) pairs
+        // go to the P buffers); then each warp merges and writes whole rows, 512 contiguous bytes
+        // per store instruction.
+        if (n_mine > 0) alive = mbar_wait(bar_o + g * 8, (n_mine - 1) & 1, a.status, qt) && alive;
         umma::fence_after_sync();
-        const size_t slot = size_t(pa.first_slot + run);
-        const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + row;
-        const float inv = (l > 0.f && alive) ? 1.f / l : 0.f;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");  // every product of either group is done
+        float2 *stats = reinterpret_cast<float2 *>(smem + OFF_P);            // [2][128]
+        float *stage = reinterpret_cast<float *>(smem + OFF_K);              // [2][128][128], 16-byte chunks swizzled
+        const float my_mu = (n_mine > 0 && alive && m_ref != -INFINITY) ? m_ref * c2 : -INFINITY;
+        stats[g * 128 + r] = make_float2(my_mu, l);
+        {
+            float *srow = stage + (g * 128 + r) * D;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
-            uint32_t r[32];
-            if (nt > 0) {
-                tmem_ld32(r, tmem_o + lane_base + c0);
-                tmem_ld_wait(r);
-            } else {
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                if (n_mine > 0) {
+                    tmem_ld32(o, tmem_og + lane_base + c0);
+                    tmem_ld_wait(o);
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = 0u;
-            }
-            if (row < n_q) {
-                float4 *dst = reinterpret_cast<float4 *>(a.part_o + prow_g * D + c0);
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;
+                }
 #pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    dst[i >> 2] = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                              __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                for (int i = 0; i < 32; i += 4) {
+                    const int chunk = (c0 + i) >> 2;
+                    *reinterpret_cast<uint4 *>(srow + ((chunk ^ (r & 7)) << 2)) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                }
             }
         }
-        if (row < n_q) a.part_lse[prow_g] = (l > 0.f && alive) ? m_ref * c2 + log2f(l) : -INFINITY;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        const size_t slot = size_t(pa.first_slot + run);
+        const int lane = tid & 31;
+#pragma unroll 1
+        for (int rr = warp; rr < QM; rr += PFX_SOFTMAX / 32) {
+            const int grow = qt * QM + rr;
+            if (grow >= n_q) break;
+            const float2 s0 = stats[rr], s1 = stats[128 + rr];
+            const float mu_all = fmaxf(s0.x, s1.x);
+            const float w0 = s0.x == -INFINITY ? 0.f : fast_exp2(s0.x - mu_all);
+            const float w1 = s1.x == -INFINITY ? 0.f : fast_exp2(s1.x - mu_all);
+            const float l_all = s0.y * w0 + s1.y * w1;
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            const float f0 = w0 * inv, f1 = w1 * inv;
+            const int sw = (lane ^ (rr & 7)) << 2;
+            const float4 v0 = *reinterpret_cast<const float4 *>(stage + rr * D + sw);
+            const float4 v1 = *reinterpret_cast<const float4 *>(stage + (128 + rr) * D + sw);
+            const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + grow;
+            reinterpret_cast<float4 *>(a.part_o + prow_g * D)[lane] =
+                make_float4(v0.x * f0 + v1.x * f1, v0.y * f0 + v1.y * f1, v0.z * f0 + v1.z * f1, v0.w * f0 + v1.w * f1);
+            if (lane == 0) a.part_lse[prow_g] = l_all > 0.f ? mu_all + log2f(l_all) : -INFINITY;
+        }
     }
 
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 4)
+    if (warp == 9)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
