@@ -3,20 +3,27 @@
 // The prefix part of the reference kernel (fstattention.py:113-136) is plain dense attention:
 // every query row attends to every prefix row.  That is the one place on this path where the
 // tiles are large and dense, so it gets its own kernel: one CTA per (128 query rows, head,
-// batch element, run of prefix rows).  Per 128-row K/V tile
-//     S = Q K^T     tcgen05.mma  M=128 N=128 K=16 x 8, both operands K-major in shared memory
-//     softmax       one thread per query row (TMEM lane = row, so no shuffles): tcgen05.ld of S,
-//                   running maximum with a lazy reference point, P written to shared memory
-//     O += P V      tcgen05.mma  A = P (K-major), B = V (MN-major: rows of V are the K index)
-// with S (two buffers of 128 columns) and O (128 columns) living in tensor memory.  K/V tiles arrive by TMA
-// (128-row x 64-column boxes, 128-byte swizzle) into two stages.  The result is a partial
-// output per run (normalised rows in fp32 plus base-2 log-sum-exp) in the layout the tree
-// kernel writes; combine_splits_kernel merges them.
+// batch element, run of prefix rows).  Per 128-row K/V tile t
+//     S(t) = Q K(t)^T       tcgen05.mma  M=128 N=128 K=16 x 8, both operands K-major in shared memory
+//     P(t) = softmax part   one thread per query row (TMEM lane = row, so no shuffles): tcgen05.ld
+//                           of S, probabilities against a lazily moved reference point, P written
+//                           to shared memory in the 128-byte-swizzled K-major layout
+//     O_g += P(t) V(t)      tcgen05.mma  A = P, B = V (MN-major: rows of V are the K index)
+// Tensor memory holds two S buffers and two accumulators O_0, O_1 (4 x 128 columns).  K/V tiles
+// arrive by TMA (128-row x 64-column boxes, 128-byte swizzle) into two stages each.
 //
-// A fifth warp's first lane issues TMA and MMA (S one tile ahead, into the other S buffer), the
-// four softmax warps talk to it through mbarriers only.  Every wait is bounded in time
-// (mbar_wait): on expiry the kernel records FST_DEV_TIMEOUT, stops issuing, frees its tensor
-// memory and returns.
+// Ten warps.  Warps 0-3 and 4-7 are two softmax groups; group g takes the tiles with t & 1 == g
+// and keeps its own reference point, row sums, P buffer and accumulator O_g, so the groups never
+// wait for one another and one group's barrier waits and tensor-memory latencies hide behind the
+// other's exponentials.  Lane 0 of warp 8 loads K and issues S(t); lane 0 of warp 9 loads V and
+// issues O_g += P V.  All hand-offs are mbarriers (TMA completion, tcgen05.commit, or arrivals by
+// the 128 threads of a group); every barrier indexed by t & 1 completes once per two tiles, so a
+// waiter can never fall two phases behind.  At the end the groups' results are merged through
+// shared memory and written as one partial result per run (normalised rows in fp32 plus base-2
+// log-sum-exp) in the layout the tree kernel writes; combine_splits_kernel merges the runs.
+//
+// Every wait is bounded in time (mbar_wait): on expiry the kernel records FST_DEV_TIMEOUT, stops
+// issuing, frees its tensor memory and returns.
 
 #include "fst_attention_tma.cuh"
 
@@ -241,7 +248,6 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         // with its own reference point and row sum, so the groups never wait for one another and
         // one group's waits and tensor-memory latencies hide behind the other's exponentials.
         const int r = tid & 127, g = tid >> 7;            // my query row (TMEM lane r) and group
-        const int row = qt * QM + r;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem_s0 + g * 128, tmem_og = tmem_o + g * 128;
         unsigned char *prow = smem + OFF_P + g * TILE + r * 128;   // my row of P buffer g
@@ -374,24 +380,35 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         asm volatile("bar.sync 1, 256;\n" ::: "memory");
         const size_t slot = size_t(pa.first_slot + run);
         const int lane = tid & 31;
-#pragma unroll 1
-        for (int rr = warp; rr < QM; rr += PFX_SOFTMAX / 32) {
-            const int grow = qt * QM + rr;
-            if (grow >= n_q) break;
+        constexpr int RPW = QM / (PFX_SOFTMAX / 32);      // 16 rows per warp: rows warp * 16 ..
+        // lanes 0..15 work out the two groups' weights for one row each; they are handed round by shuffle
+        float f0 = 0.f, f1 = 0.f;
+        {
+            const int rr = warp * RPW + (lane & (RPW - 1));
             const float2 s0 = stats[rr], s1 = stats[128 + rr];
             const float mu_all = fmaxf(s0.x, s1.x);
             const float w0 = s0.x == -INFINITY ? 0.f : fast_exp2(s0.x - mu_all);
             const float w1 = s1.x == -INFINITY ? 0.f : fast_exp2(s1.x - mu_all);
             const float l_all = s0.y * w0 + s1.y * w1;
             const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-            const float f0 = w0 * inv, f1 = w1 * inv;
+            f0 = w0 * inv;
+            f1 = w1 * inv;
+            const int grow = qt * QM + rr;
+            if (lane < RPW && grow < n_q)
+                a.part_lse[((slot * a.Z + z) * a.H + h) * n_q + grow] = l_all > 0.f ? mu_all + log2f(l_all) : -INFINITY;
+        }
+#pragma unroll 4
+        for (int i = 0; i < RPW; ++i) {
+            const int rr = warp * RPW + i, grow = qt * QM + rr;
+            const float g0 = __shfl_sync(0xffffffffu, f0, i), g1 = __shfl_sync(0xffffffffu, f1, i);
             const int sw = (lane ^ (rr & 7)) << 2;
             const float4 v0 = *reinterpret_cast<const float4 *>(stage + rr * D + sw);
             const float4 v1 = *reinterpret_cast<const float4 *>(stage + (128 + rr) * D + sw);
-            const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + grow;
-            reinterpret_cast<float4 *>(a.part_o + prow_g * D)[lane] =
-                make_float4(v0.x * f0 + v1.x * f1, v0.y * f0 + v1.y * f1, v0.z * f0 + v1.z * f1, v0.w * f0 + v1.w * f1);
-            if (lane == 0) a.part_lse[prow_g] = l_all > 0.f ? mu_all + log2f(l_all) : -INFINITY;
+            if (grow < n_q) {
+                const size_t prow_g = ((slot * a.Z + z) * a.H + h) * n_q + grow;
+                reinterpret_cast<float4 *>(a.part_o + prow_g * D)[lane] =
+                    make_float4(v0.x * g0 + v1.x * g1, v0.y * g0 + v1.y * g1, v0.z * g0 + v1.z * g1, v0.w * g0 + v1.w * g1);
+            }
         }
     }
 

@@ -49,10 +49,10 @@ def _pick_splits(kv_splits, q, prefix, block_m, kernel):
     """(runs the shared prefix is cut into, whether a workspace is needed).
 
     Only the tensor-core kernels split.  With head_dim 128 and at least 256 prefix rows the
-    prefix goes to the tcgen05 kernel (one CTA per 128 query rows, head, batch element and run;
-    the automatic choice aims at one CTA per SM, which is all its shared memory allows, in runs of at
-    least 256 rows); otherwise the tree
-    kernel walks the prefix itself, split to about four CTAs per SM."""
+    prefix goes to the tcgen05 kernel: one CTA per 128 query rows, head, batch element and run.
+    Its shared memory allows one CTA per SM, so the automatic choice is as many runs as keep the
+    grid within one wave, each at least 256 rows.  Otherwise the tree kernel walks the prefix
+    itself, split to about four CTAs per SM."""
     if q.dtype not in (torch.float16, torch.bfloat16) or q.shape[-1] not in (64, 128) \
             or block_m not in (32, 64, 128) or kernel in ("simt", "mma") or prefix <= 0:
         return 1, False

@@ -295,6 +295,60 @@ def test_prefix_split_over_ctas(fst, prefix, splits):
     assert fst.last_status() == 0
 
 
+@pytest.mark.parametrize("prefix,runs,n,dtype", [(128, 1, 256, torch.float16), (129, 2, 200, torch.float16),
+                                                  (700, 1, 256, torch.float16), (1111, 3, 130, torch.float16),
+                                                  (1111, 2, 256, torch.bfloat16)])
+def test_prefix_tcgen05_moving_maximum(fst, prefix, runs, n, dtype):
+    """The tcgen05 prefix kernel with scores that keep growing along the prefix, so that the
+    reference point of its exponentials has to move (and the accumulator in tensor memory be
+    rescaled) several times; odd and single tile counts, ragged last tiles, ragged query rows."""
+    from fstattention_b200 import configs
+    par = configs.random_window_tree(5, n, 40)
+    H, D = 2, 128
+    q, k, v = make_qkv(1, H, n, prefix + n, D, dtype, seed=41)
+    ramp = torch.linspace(0.0, 4.0, prefix).view(1, 1, prefix, 1)
+    k[:, :, :prefix] = (k[:, :, :prefix].float() * 0.05 + ramp).to(dtype)      # q.k grows by ~250 along the prefix
+    q = (q.float() * 0.05 + 0.5).to(dtype)
+    scale = D ** -0.5
+    exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
+    meta = fst.build_tree_metadata(par, 64, 128)
+    out, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel="tma_umma",
+                                 kv_splits=runs, return_lse=True)
+    tol = TOL_F16 if dtype == torch.float16 else TOL_BF16
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    assert maxabs(out.cpu(), exact) <= tol, maxabs(out.cpu(), exact)
+    one, lse_one = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel="tma_t64",
+                                     kv_splits=1, return_lse=True)
+    assert maxabs(lse, lse_one) <= (2e-3 if dtype == torch.float16 else 2e-2)
+    assert fst.last_status() == 0
+
+
+def test_prefix_tcgen05_in_a_cuda_graph(fst):
+    """The prefix path forks its tree kernel onto a second stream; captured into a CUDA graph and
+    replayed on new data it gives what the eager call gives."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D, prefix = 256, 4, 128, 1024
+    meta = fst.build_tree_metadata(par, 64, 64)
+    scale = D ** -0.5
+    q, k, v = (t.cuda() for t in make_qkv(1, H, n, prefix + n, D, torch.float16, seed=51))
+    out = torch.empty_like(q)
+    fst.fst_attention(q, k, v, meta, sm_scale=scale, kernel="tma_umma", kv_splits=2, out=out)   # warm-up, eager
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fst.fst_attention(q, k, v, meta, sm_scale=scale, kernel="tma_umma", kv_splits=2, out=out)
+    q2, k2, v2 = (t.cuda() for t in make_qkv(1, H, n, prefix + n, D, torch.float16, seed=52))
+    q.copy_(q2); k.copy_(k2); v.copy_(v2)
+    graph.replay()
+    torch.cuda.synchronize()
+    eager = fst.fst_attention(q2, k2, v2, meta, sm_scale=scale, kernel="tma_umma", kv_splits=2)
+    assert maxabs(out, eager) == 0.0
+    exact = oracle_attention(q2.cpu(), k2.cpu(), v2.cpu(), par, scale, prefix=prefix, compute_dtype=torch.float32)
+    assert maxabs(out.cpu(), exact) <= TOL_F16
+    assert fst.last_status() == 0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
