@@ -44,6 +44,7 @@ NCU_TRAFFIC_BYTES = {"medusa256": 6.36e6, "forest64": 515.7e6}
 METRIC = "tree_attn_gathered_kv_bandwidth"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TENSOR_TFLOPS = 1590.0
 
 
 def parse_args():
@@ -61,6 +62,16 @@ def parse_args():
                     help="strong scaling: split the workload's trees or heads over the ranks and "
                          "all-gather the outputs (NCCL) once per step")
     return ap.parse_args()
+
+
+def measured_tensor_peak():
+    """Dense 16-bit tensor throughput (TFLOP/s) of a kernel timed alone: the measured burst figure."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return FALLBACK_TENSOR_TFLOPS, "fallback"
 
 
 def measured_hbm_peak():
@@ -352,6 +363,20 @@ def run_ours(args, rank, world):
 
     if rank != 0:
         return
+    # A long dense prefix makes the call compute-bound: the prefix goes to the tcgen05 kernel and
+    # the bound is the tensor cores.  Algorithmic flops: every query block forms block_m x rows
+    # scores and as many products with V, 2 * head_dim flops each.
+    plan = fst.launch_plan(layers[0][0], w.prefix, w.block_m, args.kernel)
+    roofline_tensor = None
+    if "prefix_umma_kernel" in plan["kernels"]:
+        tpeak, tkind = measured_tensor_peak()
+        esize = 4 if w.dtype == "fp32" else 2
+        flops = 4.0 * D * w.block_m * (kv / (2 * D * esize))
+        tf = flops / (launch_us * 1e-6) / 1e12
+        roofline_tensor = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
+                           "traffic": None, "peak_source": f"of {tkind}", "kernel": "prefix_umma_kernel",
+                           "flops_per_call": flops, "prefix_runs": plan["prefix_runs"],
+                           "note": "time is the whole call: prefix kernel, tree kernel beside it, merge kernel"}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -367,9 +392,10 @@ def run_ours(args, rank, world):
         "precompute_us": pre_us,
         "gathered_kv_bytes_per_call": kv,
         "q_o_bytes_per_call": info["q_o_bytes_per_call"],
-        "gpu_launches": args.steps * (L + 1),
+        "gpu_launches": args.steps * (L * len(plan["kernels"]) + 1),
+        "kernels_per_call": plan["kernels"],
         "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "roofline": roofline_tensor if roofline_tensor is not None else {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name), "peak_source": f"of {peak_kind}",
                      "kernel": "attn_tma_kernel" if args.kernel in ("auto", "tma") else f"attn_{args.kernel}_kernel", "achieved_incl_q_o": (kv + info["q_o_bytes_per_call"]) / (launch_us * 1e-6) / 1e9,
                      "frac_of_nominal_8000": achieved / 8000.0},

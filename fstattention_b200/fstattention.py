@@ -74,6 +74,22 @@ def _pick_splits(kv_splits, q, prefix, block_m, kernel):
     return splits, splits > 1
 
 
+def launch_plan(q, prefix, block_m, kernel: str = "auto", kv_splits: Optional[int] = None) -> dict:
+    """Which kernels one ``fst_attention`` call on packed metadata launches for ``q`` (shape and
+    dtype only), a shared prefix of ``prefix`` rows and the given block size, mirroring the
+    dispatch inside the library: ``{"kernels": [...], "prefix_runs": r}``."""
+    splits, need_ws = _pick_splits(kv_splits, q, prefix, block_m, kernel)
+    tensor_core = q.dtype in (torch.float16, torch.bfloat16) and q.shape[-1] in (64, 128) \
+        and block_m in (16, 32, 64, 128)
+    tree = "attn_simt_kernel" if kernel == "simt" or not tensor_core else \
+        "attn_mma_kernel" if kernel == "mma" or block_m == 16 else "attn_tma_kernel"
+    if need_ws and q.shape[-1] == 128 and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
+        return {"kernels": ["prefix_umma_kernel", tree, "combine_splits_kernel"], "prefix_runs": splits}
+    if need_ws:
+        return {"kernels": [tree, "combine_splits_kernel"], "prefix_runs": splits}
+    return {"kernels": [tree], "prefix_runs": 1}
+
+
 def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_scale=None,
                   BLOCK_M=128, MAX_ANCESTORS=64, *, out: Optional[torch.Tensor] = None,
                   return_lse: bool = False, kernel: str = "auto", kv_splits: Optional[int] = None):
