@@ -170,7 +170,7 @@ size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, 
 }
 
 static int attention_fwd_impl(const void *q, const void *k, const void *v, void *o, float *lse,
-                      const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
+                      const void *packed, size_t meta_tree_stride, int Z, int H, int H_kv, int n_q, int n_kv,
                       int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
                       int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
                       int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
@@ -184,6 +184,7 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128)
         return FST_ERR_UNSUPPORTED;                       // the reference's set, fstattention.py:157
     if (H > 65535 || Z > 65535) return FST_ERR_TOO_LARGE;
+    if (H_kv <= 0 || H % H_kv != 0) return FST_ERR_INVALID_ARG;
     if (!aligned16(packed) || (meta_tree_stride & 15)) return FST_ERR_ALIGNMENT;
 
     AttnArgs a;
@@ -191,6 +192,7 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     a.packed = static_cast<const unsigned char *>(packed);
     a.meta_stride = meta_tree_stride;
     a.Z = Z; a.H = H; a.n_q = n_q; a.n_kv = n_kv; a.D = head_dim; a.prefix = n_kv - n_q;
+    a.kv_group = H / H_kv;
     a.qs_z = q_stride_z; a.qs_h = q_stride_h; a.qs_n = q_stride_n;
     a.ks_z = k_stride_z; a.ks_h = k_stride_h; a.ks_n = k_stride_n;
     a.vs_z = v_stride_z; a.vs_h = v_stride_h; a.vs_n = v_stride_n;
@@ -280,7 +282,7 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
                       int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
                       int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
                       void *stream) {
-    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, n_q, n_kv, head_dim,
+    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, H, n_q, n_kv, head_dim,
                               q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
                               v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
                               block_m, max_ancestors, sm_scale, dtype, kernel, 1, nullptr, 0, status,
@@ -298,7 +300,25 @@ int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void 
                               size_t workspace_bytes, int32_t *status, void *stream) {
     if (kv_splits < 1) return FST_ERR_INVALID_ARG;
     if (kv_splits > 1 && (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
-    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, n_q, n_kv, head_dim,
+    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, H, n_q, n_kv, head_dim,
+                              q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                              v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
+                              block_m, max_ancestors, sm_scale, dtype, kernel, kv_splits, workspace,
+                              workspace_bytes, status, stream);
+}
+
+int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, float *lse,
+                          const void *packed, size_t meta_tree_stride, int Z, int H, int H_kv, int n_q,
+                          int n_kv, int head_dim, int64_t q_stride_z, int64_t q_stride_h,
+                          int64_t q_stride_n, int64_t k_stride_z, int64_t k_stride_h,
+                          int64_t k_stride_n, int64_t v_stride_z, int64_t v_stride_h,
+                          int64_t v_stride_n, int64_t o_stride_z, int64_t o_stride_h,
+                          int64_t o_stride_n, int block_m, int max_ancestors, float sm_scale,
+                          int dtype, int kernel, int kv_splits, void *workspace,
+                          size_t workspace_bytes, int32_t *status, void *stream) {
+    if (kv_splits < 1) return FST_ERR_INVALID_ARG;
+    if (kv_splits > 1 && (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
+    return attention_fwd_impl(q, k, v, o, lse, packed, meta_tree_stride, Z, H, H_kv, n_q, n_kv, head_dim,
                               q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
                               v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
                               block_m, max_ancestors, sm_scale, dtype, kernel, kv_splits, workspace,

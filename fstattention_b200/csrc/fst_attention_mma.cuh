@@ -138,8 +138,9 @@ attn_mma_kernel(const AttnArgs a) {
     int count = __ldg(reinterpret_cast<const int32_t *>(blob + L.off_count) + b);
 
     const T *qp = static_cast<const T *>(a.q) + z * a.qs_z + h * a.qs_h;
-    const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
-    const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + h * a.vs_h;
+    const int hk = h / a.kv_group;                        // my K/V head
+    const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + hk * a.ks_h;
+    const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + hk * a.vs_h;
     T *op = static_cast<T *>(a.o) + z * a.os_z + h * a.os_h;
 
     const int lr = tid / CH, lc = tid % CH;               // my row-in-pass and 16-byte chunk

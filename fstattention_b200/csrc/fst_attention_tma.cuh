@@ -151,8 +151,9 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     const uint32_t *g_bmask = reinterpret_cast<const uint32_t *>(blob + L.off_bmask) + size_t(b) * BM * BW;
     const int count = tree ? __ldg(reinterpret_cast<const int32_t *>(blob + L.off_count) + b) : 0;
 
-    const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + h * a.ks_h;
-    const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + h * a.vs_h;
+    const int hk = h / a.kv_group;                        // my K/V head
+    const T *kp = static_cast<const T *>(a.k) + z * a.ks_z + hk * a.ks_h;
+    const T *vp = static_cast<const T *>(a.v) + z * a.vs_z + hk * a.vs_h;
     const int lr = tid / CH, lc = tid % CH;               // my row-in-pass and 16-byte chunk
     const int r0 = warp * 16 + g, r1 = r0 + 8;            // my two rows inside the block
     const bool ok0 = row0 + r0 < n_q, ok1 = row0 + r1 < n_q;
@@ -181,7 +182,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int hf = 0; hf < TL::HALVES; ++hf) {
                 if (tree)
-                    tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, h, z, bar_qk);
+                    tma_load_4d(s_base + SM::KB + j * SM::TILE + hf * 4096, &tm_k, hf * 64, prefix + row0 + j * 32, hk, z, bar_qk);
                 tma_load_4d(s_base + SM::QO + j * SM::TILE + hf * 4096, &tm_q, hf * 64, row0 + j * 32, h, z, bar_qk);
             }
         if (tree) {
@@ -190,7 +191,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             for (int j = 0; j < NB32; ++j)
 #pragma unroll
                 for (int hf = 0; hf < TL::HALVES; ++hf)
-                    tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, h, z, bar_v);
+                    tma_load_4d(s_base + SM::VB + j * SM::TILE + hf * 4096, &tm_v, hf * 64, prefix + row0 + j * 32, hk, z, bar_v);
         }
     }
 
@@ -219,8 +220,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             for (int tp = 0; tp < TP; ++tp)
 #pragma unroll
                 for (int hf = 0; hf < TL::HALVES; ++hf) {
-                    tma_load_4d(kd + tp * SM::TILE + hf * 4096, &tm_k, hf * 64, p0 + tp * 32, h, z, bar);
-                    tma_load_4d(vd + tp * SM::TILE + hf * 4096, &tm_v, hf * 64, p0 + tp * 32, h, z, bar);
+                    tma_load_4d(kd + tp * SM::TILE + hf * 4096, &tm_k, hf * 64, p0 + tp * 32, hk, z, bar);
+                    tma_load_4d(vd + tp * SM::TILE + hf * 4096, &tm_v, hf * 64, p0 + tp * 32, hk, z, bar);
                 }
         }
     };
@@ -585,8 +586,8 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
     constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
     alignas(64) CUtensorMap tq, tk, tv, to;
     if (!make_map(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
-        !make_map(&tk, a.k, bf16, D, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
+        !make_map(&tk, a.k, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
         !make_map(&to, a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z))
         return cudaErrorNotSupported;
     static bool configured_on[kMaxDevices] = {};           // the attribute is per device

@@ -71,6 +71,7 @@ struct AttnArgs {
     const unsigned char *packed;
     size_t meta_stride;
     int Z, H, n_q, n_kv, D, prefix;
+    int kv_group;          // query heads per K/V head (grouped-query attention); K and V have H / kv_group heads
     int64_t qs_z, qs_h, qs_n, ks_z, ks_h, ks_n, vs_z, vs_h, vs_n, os_z, os_h, os_n;
     int bm, ma, nb;
     float scale_log2;      // sm_scale * log2(e)

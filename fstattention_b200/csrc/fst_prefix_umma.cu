@@ -127,7 +127,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem = smem_raw + (s_base - smem_u32(smem_raw));
-    const int qt = blockIdx.x, h = blockIdx.y;
+    const int qt = blockIdx.x, h = blockIdx.y, hk = h / a.kv_group;   // query tile, head, K/V head
     const int z = blockIdx.z / pa.n_runs, run = blockIdx.z - z * pa.n_runs;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int prefix = a.prefix, n_q = a.n_q;
@@ -150,14 +150,14 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     auto load_k = [&](int t) {
         const uint32_t bar = bar_k + (t & 1) * 8;
         mbar_arrive_expect_tx(bar, TILE);
-        tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, h, z, bar);
-        tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, h, z, bar);
+        tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, hk, z, bar);
+        tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, hk, z, bar);
     };
     auto load_v = [&](int t) {
         const uint32_t bar = bar_v + (t & 1) * 8;
         mbar_arrive_expect_tx(bar, TILE);
-        tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, h, z, bar);
-        tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, h, z, bar);
+        tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, hk, z, bar);
+        tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, hk, z, bar);
     };
     if (tid == PFX_SOFTMAX) {
         mbar_init(bar_q, 1);
@@ -438,8 +438,8 @@ static cudaError_t launch_prefix_t(const AttnArgs &a, int n_runs, int first_slot
     constexpr bool bf16 = !std::is_same<T, __half>::value;
     alignas(64) CUtensorMap tq, tk, tv;
     if (!make_map_rows128(&tq, a.q, bf16, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
-        !make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-        !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H, a.Z, a.vs_n, a.vs_h, a.vs_z))
+        !make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+        !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z))
         return cudaErrorNotSupported;
     static bool configured_on[kMaxDevices] = {};
     const int slot = current_device_slot();

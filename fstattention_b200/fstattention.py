@@ -101,7 +101,8 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     absolute K/V rows, i.e. the caller adds the prefix length as fstattention.py:211-212 does.
     Alternatively pass a ``TreeMetadata`` as ``ancestor_idx`` and leave the other two ``None``;
     its block size and ancestor bound are used.  Metadata with a leading tree dimension of size
-    ``Z`` gives every batch element its own tree.
+    ``Z`` gives every batch element its own tree.  ``k`` and ``v`` may have fewer heads than ``q``
+    (grouped-query attention, ``H`` a multiple of ``H_kv``; packed metadata only).
 
     ``kv_splits`` cuts a shared prefix into that many runs handled by separate CTAs and merged
     afterwards (packed metadata only); ``None`` picks a split that fills the GPU when the tree
@@ -119,9 +120,9 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise TypeError("q, k, v must share one dtype out of float16, bfloat16, float32")
     Z, H, n_q, D = q.shape
-    n_kv = k.shape[2]
-    if k.shape != (Z, H, n_kv, D) or v.shape != k.shape or n_kv < n_q:
-        raise ValueError("k and v must be [Z, H, P + N, D] with P >= 0")
+    n_kv, H_kv = k.shape[2], k.shape[1]
+    if k.shape != (Z, H_kv, n_kv, D) or v.shape != k.shape or n_kv < n_q or H_kv < 1 or H % H_kv:
+        raise ValueError("k and v must be [Z, H_kv, P + N, D] with P >= 0 and H a multiple of H_kv")
     o = torch.empty_like(q) if out is None else out
     if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
         raise ValueError("out must match q")
@@ -151,16 +152,20 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
             if need_ws:
                 ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, splits))
                 ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-            rc = lib.fst_attention_fwd_splitkv(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                lse.data_ptr() if lse is not None else None,
-                meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0,
-                *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern,
-                splits, ws.data_ptr() if ws is not None else None, ws_bytes,
-                status.data_ptr(), stream)
+            tail = (BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern, splits,
+                    ws.data_ptr() if ws is not None else None, ws_bytes, status.data_ptr(), stream)
+            head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                    lse.data_ptr() if lse is not None else None,
+                    meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0)
+            if H_kv == H:
+                rc = lib.fst_attention_fwd_splitkv(*head, *common_shape, *tail)
+            else:                                         # grouped-query attention
+                rc = lib.fst_attention_fwd_gqa(*head, Z, H, H_kv, *common_shape[2:], *tail)
             _lib.check(rc, "fst_attention_fwd")
         else:
             ai, am, li = ancestor_idx, ancestor_mask, leaf_idx
+            if H_kv != H:
+                raise ValueError("grouped-query attention needs packed metadata (build_tree_metadata)")
             if am is None or li is None:
                 raise TypeError("ancestor_mask and leaf_idx are required with plain tensors")
             if not (ai.is_cuda and am.is_cuda and li.is_cuda):

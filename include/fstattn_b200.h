@@ -162,6 +162,26 @@ int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void 
                               int32_t *status, void *stream);
 
 /*
+ * fst_attention_fwd_splitkv for grouped-query attention: q and o have H heads, k and v have H_kv
+ * heads, H a multiple of H_kv; query head h reads K/V head h / (H / H_kv).  The reference assumes
+ * H_kv == H (fstattention.py:44-45 index K and V with the query's head offset); this is the
+ * layout of the KV caches the kernel meets in a decoder.  Query heads of one group sit in
+ * neighbouring CTAs, so their shared K/V rows are fetched from HBM once and from L2 afterwards.
+ * workspace as for fst_attention_fwd_splitkv (sized by H); kv_splits = 1 and workspace = NULL
+ * give the plain single-kernel call.
+ */
+int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, float *lse,
+                          const void *packed, size_t meta_tree_stride,
+                          int Z, int H, int H_kv, int n_q, int n_kv, int head_dim,
+                          int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                          int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                          int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                          int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                          int block_m, int max_ancestors, float sm_scale, int dtype, int kernel,
+                          int kv_splits, void *workspace, size_t workspace_bytes,
+                          int32_t *status, void *stream);
+
+/*
  * The same with reference-format metadata, i.e. exactly the arguments of the reference's
  * fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale, BLOCK_M,
  * MAX_ANCESTORS) (fstattention.py:153).  Index tensors hold absolute K/V rows

@@ -349,6 +349,35 @@ def test_prefix_tcgen05_in_a_cuda_graph(fst):
     assert fst.last_status() == 0
 
 
+@pytest.mark.parametrize("prefix", [0, 512])
+def test_grouped_query_attention(fst, prefix):
+    """K and V with fewer heads than Q: query head h reads K/V head h // (H / H_kv).  Checked
+    against the oracle on K/V with the heads repeated, for every kernel, with and without a
+    shared prefix (where the tcgen05 prefix kernel and the split tree kernel take part)."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, H_kv, D = 256, 8, 2, 128
+    q, _, _ = make_qkv(2, H, n, prefix + n, D, torch.float16, seed=61)
+    _, k, v = make_qkv(2, H_kv, n, prefix + n, D, torch.float16, seed=62)
+    scale = D ** -0.5
+    k_rep, v_rep = (t.repeat_interleave(H // H_kv, dim=1) for t in (k, v))
+    exact = oracle_attention(q, k_rep, v_rep, par, scale, prefix=prefix, compute_dtype=torch.float32)
+    meta = fst.build_tree_metadata(par, 64, 64)
+    kernels = ["auto", "simt", "mma", "tma_t32", "tma_t64"] + (["tma_umma"] if prefix else [])
+    for kern in kernels:
+        for splits in ((1, 2) if prefix and kern not in ("simt", "mma") else (None,)):
+            out, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern,
+                                         kv_splits=splits, return_lse=True)
+            assert maxabs(out.cpu(), exact) <= TOL_F16, (kern, splits, maxabs(out.cpu(), exact))
+            same = fst.fst_attention(q.cuda(), k_rep.cuda(), v_rep.cuda(), meta, sm_scale=scale, kernel=kern,
+                                     kv_splits=splits)
+            assert torch.equal(out, same), (kern, splits)      # the same arithmetic on the same rows
+    with pytest.raises(ValueError):
+        fst.fst_attention(q.cuda(), k[:, :1].repeat(1, 3, 1, 1).cuda(), v[:, :1].repeat(1, 3, 1, 1).cuda(), meta,
+                          sm_scale=scale)                       # 8 query heads over 3 K/V heads
+    assert fst.last_status() == 0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
