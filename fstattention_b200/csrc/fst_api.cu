@@ -148,6 +148,14 @@ int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m,
                                          static_cast<cudaStream_t>(stream)));
 }
 
+int fst_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
+                  int32_t *new_parent, int32_t *status, void *stream) {
+    if (!parent || !order || !new_parent || n_trees <= 0 || n_nodes <= 0) return FST_ERR_INVALID_ARG;
+    if (n_nodes > 8192 || n_trees > 65535) return FST_ERR_TOO_LARGE;
+    return cuda_status(launch_dfs_order(parent, n_trees, n_nodes, order, new_parent, status,
+                                        static_cast<cudaStream_t>(stream)));
+}
+
 int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
                       const int64_t *leaf_idx, int n_trees, int n_blocks, int block_m,
                       int max_ancestors, int64_t index_base, void *packed,

@@ -119,7 +119,6 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     constexpr int RPP = NT / CH;          // rows covered by one pass of all threads
     constexpr int SPT = TN / RPP;         // gathered rows per thread and tile
     constexpr int NB32 = SM::NB32;
-    constexpr int NBLK = SM::NBT;
     constexpr int TP = SM::TP;            // 32-row physical tiles (= mask words) per column tile
     constexpr int NG = TN / 16;           // 16-column groups per column tile
     constexpr int BW = (BM + 31) / 32;

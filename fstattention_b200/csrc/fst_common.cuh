@@ -60,6 +60,9 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
                               void *packed, size_t packed_stride, int32_t *status,
                               cudaStream_t stream);
 
+cudaError_t launch_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
+                             int32_t *new_parent, int32_t *status, cudaStream_t stream);
+
 cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
                         int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
                         size_t packed_stride, int32_t *status, cudaStream_t stream);

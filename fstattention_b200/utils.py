@@ -291,3 +291,34 @@ def dfs_order(parent: Sequence[int]):
     order[pos] = np.arange(n)
     new_parent = np.where(par[order] >= 0, pos[np.clip(par[order], 0, None)], -1)
     return order.tolist(), new_parent.tolist()
+
+
+def dfs_order_device(parent: TreeLike, *, check: bool = True,
+                     device: Union[str, torch.device, None] = None):
+    """``dfs_order`` computed on the GPU with one kernel launch on the current stream, for parent
+    arrays that already live there (a decoder that builds its tree on the device).
+
+    ``parent`` is ``[N]`` or ``[T, N]`` as for ``build_tree_metadata`` (N <= 8192).  Returns
+    ``(order, new_parent)`` as int32 CUDA tensors of the same shape, with the meaning
+    ``dfs_order`` gives them; ``new_parent`` goes straight into ``build_tree_metadata``.
+    ``check=False`` skips reading the status record (no device synchronisation); a malformed
+    tree then leaves both outputs uninitialised."""
+    if device is None:
+        device = parent.device if torch.is_tensor(parent) and parent.is_cuda else "cuda"
+    par = _as_parent_tensor(parent, device)
+    n_trees, n_nodes = (par.shape if par.dim() == 2 else (1, par.shape[0]))
+    order = torch.empty_like(par)
+    new_parent = torch.empty_like(par)
+    status = torch.zeros(_lib.STATUS_WORDS, dtype=torch.int32, device=par.device)
+    with torch.cuda.device(par.device):
+        rc = _lib.lib().fst_dfs_order(par.data_ptr(), n_trees, n_nodes, order.data_ptr(), new_parent.data_ptr(),
+                                      status.data_ptr(), torch.cuda.current_stream(par.device).cuda_stream)
+    _lib.check(rc, "fst_dfs_order")
+    if check:
+        code, where, detail, _ = status.tolist()
+        if code == _lib.DEV_MALFORMED_TREE:
+            raise ValueError(f"parent[{where}] = {detail} is neither -1 nor an earlier node")
+        if code != 0:
+            raise RuntimeError(f"fst_dfs_order: device status {code}")
+    return order, new_parent
+

@@ -100,6 +100,19 @@ int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m,
                    int32_t *status, void *stream);
 
 /*
+ * Depth-first renumbering of n_trees trees of n_nodes nodes each (parent as for fst_precompute),
+ * the node ordering the reference leaves open (README.md:19-20; utils.py:104-129 takes the
+ * caller's numbering).  order[t][i] = old index of the node that becomes node i of tree t
+ * (pre-order, children in their old relative order); new_parent[t][i] = its parent in the new
+ * numbering (< i, or -1), ready for fst_precompute.  The caller permutes the tree rows of
+ * q/k/v with `order` and scatters the output rows back.  n_nodes <= 8192 (FST_ERR_TOO_LARGE
+ * beyond); a malformed parent sets FST_DEV_MALFORMED_TREE in `status` and leaves the outputs
+ * untouched.  All pointers are device pointers.
+ */
+int fst_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
+                  int32_t *new_parent, int32_t *status, void *stream);
+
+/*
  * Convert reference-format metadata (the three tensors of utils.py:104-129, already on the
  * device) into packed blobs.  index_base is subtracted from every index; entries below it
  * are padding.  The reference's test shifts the index tensors by the prefix length,

@@ -170,3 +170,52 @@ def test_pack_kernel_round_trip(fst, metadata_golden):
             ref_parts = decode_packed(ref.cpu().numpy(), nb, bm, ma)
             for g, r in zip(got_parts, ref_parts):
                 assert np.array_equal(g, r), (name, base)
+
+
+def _reorder_cases():
+    import random
+    from fstattention_b200 import configs
+    cases = {
+        "single": [-1],
+        "chain": [-1] + list(range(99)),
+        "star": [-1] + [0] * 200,
+        "forest_of_roots": [-1] * 40,
+        "two_roots_interleaved": [-1, -1, 0, 1, 0, 1, 2, 3, 2, 3],
+        "binary31": configs.binary_tree(),
+        "medusa256": configs.workload("medusa256").trees[0],
+        "random1024": configs.random_window_tree(3, 1024, 64),
+        "wide_window": configs.random_window_tree(9, 700, 200),
+        "deep4096": configs.workload("deep4096").trees[0],
+    }
+    rng = random.Random(5)
+    cases["random8192"] = [-1] + [rng.randint(-1 if i % 97 == 0 else 0, i - 1) for i in range(1, 8192)]
+    return cases
+
+
+@pytest.mark.parametrize("name", list(_reorder_cases()))
+def test_dfs_order_device_equals_host(fst, name):
+    """The device renumbering is the host one, element for element."""
+    par = _reorder_cases()[name]
+    want_order, want_parent = fst.dfs_order(par)
+    order, new_parent = fst.dfs_order_device(par)
+    assert order.dtype == torch.int32 and order.is_cuda
+    assert order.cpu().tolist() == want_order
+    assert new_parent.cpu().tolist() == want_parent
+
+
+def test_dfs_order_device_batch_and_errors(fst):
+    from fstattention_b200 import configs
+    trees = configs.workload("forest64").trees
+    order, new_parent = fst.dfs_order_device(trees)
+    assert order.shape == (64, 256)
+    for t in (0, 17, 63):
+        want_order, want_parent = fst.dfs_order(trees[t])
+        assert order[t].cpu().tolist() == want_order and new_parent[t].cpu().tolist() == want_parent
+    # the renumbered parents feed the precompute directly and need no more ancestors than before
+    meta = fst.build_tree_metadata(new_parent, 64, 64)
+    assert meta.check() is meta
+    with pytest.raises(ValueError):
+        fst.dfs_order_device([-1, 0, 5, 1])                  # parent after the node
+    with pytest.raises(RuntimeError):
+        fst.dfs_order_device([-1] + [0] * 8192)              # more nodes than the kernel holds
+
