@@ -167,6 +167,17 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     };
     fetch_idx(0, nodeA);
     fetch_idx(1, nodeB);
+    // The mask words of the first column tile (the block's own rows) are asked for here, a
+    // global-memory latency before the first product needs them.
+    uint32_t w0n[TP], w1n[TP];
+#pragma unroll
+    for (int p = 0; p < TP; ++p) {
+        w0n[p] = w1n[p] = 0u;
+        if (tree && p < BW) {
+            if (ok0) w0n[p] = __ldg(g_bmask + r0 * BW + p);
+            if (ok1) w1n[p] = __ldg(g_bmask + r1 * BW + p);
+        }
+    }
 
     // ---- one thread starts the TMA transfers: Q and block K on one barrier, block V on another
     if (tid == 0) {
@@ -280,8 +291,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             }
         }
     };
-    uint32_t w0n[TP], w1n[TP];
-    mask_words(0, w0n, w1n);
+    if (!tree) mask_words(0, w0n, w1n);                  // no block tile: the first tile is a prefix tile
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < nblk;
