@@ -105,7 +105,7 @@ struct TmaSmem {
 // PFX = false compiles the shared-prefix machinery (dense tiles, split over CTAs) out: the
 // no-prefix kernel is smaller, and for a latency-bound kernel fewer instruction bytes is time.
 template <typename T, int D, int BM, int TN, bool PFX>
-__global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : 1))
+__global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : (BM == 128 && D == 64 && TN == 32 ? 2 : 1)))
 attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_o) {
@@ -167,16 +167,14 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     };
     fetch_idx(0, nodeA);
     fetch_idx(1, nodeB);
-    // The mask words of the first column tile (the block's own rows) are asked for here, a
-    // global-memory latency before the first product needs them.
-    uint32_t w0n[TP], w1n[TP];
+    // All mask words of the block's own rows are asked for here, a global-memory latency before
+    // the first product needs them (a block tile that turns out empty for this warp is skipped
+    // in less time than a load takes); gathered tiles fetch theirs one tile ahead.
+    uint32_t wb0[BW], wb1[BW];
 #pragma unroll
-    for (int p = 0; p < TP; ++p) {
-        w0n[p] = w1n[p] = 0u;
-        if (tree && p < BW) {
-            if (ok0) w0n[p] = __ldg(g_bmask + r0 * BW + p);
-            if (ok1) w1n[p] = __ldg(g_bmask + r1 * BW + p);
-        }
+    for (int p = 0; p < BW; ++p) {
+        wb0[p] = (tree && ok0) ? __ldg(g_bmask + r0 * BW + p) : 0u;
+        wb1[p] = (tree && ok1) ? __ldg(g_bmask + r1 * BW + p) : 0u;
     }
 
     // ---- one thread starts the TMA transfers: Q and block K on one barrier, block V on another
@@ -272,34 +270,42 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     const float c2 = a.scale_log2;
 
     const int n_tiles = nblk + nt_gat;
-    // mask words of my two rows for column tile i (fetched one tile ahead of their use)
-    auto mask_words = [&](int i, uint32_t (&w0)[TP], uint32_t (&w1)[TP]) {
+    // mask words of my two rows for gathered tile e (external ancestors, then prefix tiles)
+    auto gathered_words = [&](int e, uint32_t (&w0)[TP], uint32_t (&w1)[TP]) {
 #pragma unroll
         for (int p = 0; p < TP; ++p) {
             w0[p] = w1[p] = 0u;
-            if (i < nblk) {
-                const int wi = i * TP + p;
-                if (ok0 && wi < BW) w0[p] = __ldg(g_bmask + r0 * BW + wi);
-                if (ok1 && wi < BW) w1[p] = __ldg(g_bmask + r1 * BW + wi);
-            } else if (i - nblk < nt_ext) {
-                const int wi = (i - nblk) * TP + p;
+            if (e < nt_ext) {
+                const int wi = e * TP + p;
                 if (ok0 && wi < maw) w0[p] = __ldg(g_emask + r0 * maw + wi);
                 if (ok1 && wi < maw) w1[p] = __ldg(g_emask + r1 * maw + wi);
-            } else if (i < n_tiles) {
-                const int rem = p_end - p_lo - (i - nblk - nt_ext) * TN - p * 32;
+            } else if (e < nt_gat) {
+                const int rem = p_end - p_lo - (e - nt_ext) * TN - p * 32;
                 w0[p] = w1[p] = rem >= 32 ? 0xffffffffu : (rem > 0 ? (1u << rem) - 1u : 0u);
             }
         }
     };
-    if (!tree) mask_words(0, w0n, w1n);                  // no block tile: the first tile is a prefix tile
+    uint32_t w0n[TP], w1n[TP];                            // words of the next gathered tile
+    if (nblk == 0) gathered_words(0, w0n, w1n);
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < nblk;
         const int e = i - nblk;                           // gathered tile number
-        uint32_t w0[TP], w1[TP];
+        uint32_t w0[TP], w1[TP];                          // mask words of my two rows for this column tile
 #pragma unroll
-        for (int p = 0; p < TP; ++p) { w0[p] = w0n[p]; w1[p] = w1n[p]; }
-        mask_words(i + 1, w0n, w1n);
+        for (int p = 0; p < TP; ++p) {
+            if (blk) {
+                const int wi = i * TP + p;
+                w0[p] = w1[p] = 0u;
+#pragma unroll
+                for (int q = 0; q < BW; ++q)
+                    if (q == wi) { w0[p] = wb0[q]; w1[p] = wb1[q]; }
+            } else {
+                w0[p] = w0n[p];
+                w1[p] = w1n[p];
+            }
+        }
+        if (e + 1 >= 0) gathered_words(e + 1, w0n, w1n);  // from the last block tile on
         uint32_t kbase, vbase;
         if (blk) {
             kbase = s_base + SM::KB + i * TP * SM::TILE;
