@@ -7,8 +7,8 @@ Public surface (mirrors the reference's utils.py / fstattention.py):
 from .utils import (DEPTH_MAPPING, MAX_ANCESTOR_MAPPING, TreeMetadata, build_tree_metadata,  # noqa: F401
                     create_fst_attention_kernel_inputs, create_full_attention_mask, create_tree,
                     dfs_order, dfs_order_device, lineage_from_parent, parent_from_lineage)
-from .fstattention import fst_attention, last_status, launch_plan  # noqa: F401
+from .fstattention import fst_attention, fst_attention_paged, last_status, launch_plan  # noqa: F401
 
 __all__ = ["DEPTH_MAPPING", "MAX_ANCESTOR_MAPPING", "create_tree", "create_full_attention_mask",
            "TreeMetadata", "build_tree_metadata", "create_fst_attention_kernel_inputs",
-           "lineage_from_parent", "parent_from_lineage", "dfs_order", "dfs_order_device", "fst_attention", "last_status", "launch_plan"]
+           "lineage_from_parent", "parent_from_lineage", "dfs_order", "dfs_order_device", "fst_attention", "fst_attention_paged", "last_status", "launch_plan"]

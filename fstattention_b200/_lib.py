@@ -21,7 +21,8 @@ DEV_MALFORMED_TREE, DEV_ANCESTOR_OVERFLOW, DEV_INDEX_RANGE = 16, 17, 18
 EXPORTS = ("fst_version", "fst_status_string", "fst_packed_meta_bytes", "fst_precompute",
            "fst_pack_metadata", "fst_attention_fwd", "fst_attention_ref_workspace_bytes",
            "fst_attention_fwd_ref", "fst_attention_fwd_ref_static",
-           "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv", "fst_attention_fwd_gqa", "fst_dfs_order")
+           "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv", "fst_attention_fwd_gqa", "fst_dfs_order",
+           "fst_attention_fwd_paged")
 STATIC_SCRATCH_BYTES = 512 * 1024
 
 _lib = None
@@ -51,6 +52,10 @@ def _declare(lib):
                                               + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _i, _p, _sz, _p, _p])
     lib.fst_dfs_order.restype = _i
     lib.fst_dfs_order.argtypes = [_p, _i, _i, _p, _p, _p, _p]
+    lib.fst_attention_fwd_paged.restype = _i
+    lib.fst_attention_fwd_paged.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _p, _p, _p, _i, _p, _i, _i, _i,
+                                             _i64, _i64, _i64, _i, _i, _i, _i, _i]
+                                            + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _sz, _p, _p])
     lib.fst_attention_fwd_gqa.restype = _i
     lib.fst_attention_fwd_gqa.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i, _i]
                                           + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _i, _p, _sz, _p, _p])

@@ -333,6 +333,77 @@ int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, 
                               workspace_bytes, status, stream);
 }
 
+int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tree, void *o, float *lse,
+                            const void *packed, size_t meta_tree_stride, const void *k_pool,
+                            const void *v_pool, const int32_t *block_table, int table_stride,
+                            const int32_t *prefix_lens, int max_prefix, int page_size, int n_pages,
+                            int64_t pool_stride_page, int64_t pool_stride_row, int64_t pool_stride_head,
+                            int Z, int H, int H_kv, int n_q, int head_dim, int64_t q_stride_z,
+                            int64_t q_stride_h, int64_t q_stride_n, int64_t k_stride_z, int64_t k_stride_h,
+                            int64_t k_stride_n, int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                            int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
+                            int max_ancestors, float sm_scale, int dtype, int kv_splits, void *workspace,
+                            size_t workspace_bytes, int32_t *status, void *stream) {
+    if (!q || !k_tree || !v_tree || !o || !packed || !k_pool || !v_pool || !block_table || !prefix_lens ||
+        !workspace || Z <= 0 || H <= 0 || H_kv <= 0 || H % H_kv != 0 || n_q <= 0 || block_m <= 0 ||
+        max_ancestors <= 0 || max_prefix <= 0 || n_pages <= 0 || kv_splits < 1 || table_stride <= 0)
+        return FST_ERR_INVALID_ARG;
+    if (head_dim != 128 || !mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
+    if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return FST_ERR_UNSUPPORTED;
+    if (H > 65535 || Z > 65535 || (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
+    if ((long long)table_stride * page_size < max_prefix) return FST_ERR_INVALID_ARG;
+    const int64_t strides[] = {q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                               v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
+                               pool_stride_page, pool_stride_row, pool_stride_head};
+    bool ok = aligned16(q) && aligned16(k_tree) && aligned16(v_tree) && aligned16(o) && aligned16(k_pool) &&
+              aligned16(v_pool) && aligned16(packed) && aligned16(workspace) && !(meta_tree_stride & 15);
+    for (int64_t s : strides)
+        if ((s * 2) & 15) ok = false;
+    if (!ok) return FST_ERR_ALIGNMENT;
+    if (workspace_bytes < fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits))
+        return FST_ERR_WORKSPACE;
+
+    AttnArgs a;                                           // the tree part: K/V rows of the tree nodes only
+    a.q = q; a.k = k_tree; a.v = v_tree; a.o = o; a.lse = lse;
+    a.packed = static_cast<const unsigned char *>(packed);
+    a.meta_stride = meta_tree_stride;
+    a.Z = Z; a.H = H; a.n_q = n_q; a.n_kv = n_q; a.D = head_dim; a.prefix = 0;
+    a.kv_group = H / H_kv;
+    a.qs_z = q_stride_z; a.qs_h = q_stride_h; a.qs_n = q_stride_n;
+    a.ks_z = k_stride_z; a.ks_h = k_stride_h; a.ks_n = k_stride_n;
+    a.vs_z = v_stride_z; a.vs_h = v_stride_h; a.vs_n = v_stride_n;
+    a.os_z = o_stride_z; a.os_h = o_stride_h; a.os_n = o_stride_n;
+    a.bm = block_m; a.ma = max_ancestors; a.nb = (n_q + block_m - 1) / block_m;
+    a.scale_log2 = sm_scale * 1.4426950408889634f;
+    a.status = status;
+    a.n_splits = 1;
+    a.skip_prefix = 1;
+    a.part_slots = kv_splits + 1;
+    a.part_o = static_cast<float *>(workspace);
+    a.part_lse = a.part_o + size_t(a.part_slots) * Z * H * n_q * head_dim;
+    AttnArgs ap = a;                                      // the prefix part: rows come from the page pool
+    ap.prefix = max_prefix;
+    PagedArgs pg{k_pool, v_pool, block_table, prefix_lens, table_stride, page_size, n_pages,
+                 pool_stride_page, pool_stride_row, pool_stride_head};
+
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SideStream *side = side_stream(st);                   // as in the contiguous prefix path
+    cudaStream_t tree_st = st;
+    if (side != nullptr && cudaEventRecord(side->fork, st) == cudaSuccess &&
+        cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+        tree_st = side->stream;
+    cudaError_t e = launch_prefix_umma_paged(ap, pg, dtype, kv_splits, 1, st);
+    const cudaError_t et = launch_attention_mma(a, dtype, FST_KERNEL_TMA, tree_st);
+    if (tree_st != st) {
+        cudaError_t ej = cudaEventRecord(side->join, tree_st);
+        if (ej == cudaSuccess) ej = cudaStreamWaitEvent(st, side->join, 0);
+        if (e == cudaSuccess) e = ej;
+    }
+    if (e == cudaSuccess) e = et;
+    if (e == cudaSuccess) e = launch_combine(a, dtype, st);
+    return cuda_status(e);
+}
+
 size_t fst_attention_ref_workspace_bytes(int n_meta_trees, int n_q, int block_m, int max_ancestors) {
     if (n_meta_trees <= 0 || n_q <= 0 || block_m <= 0 || max_ancestors <= 0) return 0;
     const int nb = (n_q + block_m - 1) / block_m;

@@ -640,8 +640,9 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
 
 template <typename T, int D, int BM, int TN>
 cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
-    return a.prefix > 0 ? launch_tma_pfx<T, D, BM, TN, true>(a, stream)
-                        : launch_tma_pfx<T, D, BM, TN, false>(a, stream);
+    // the prefix instantiation also writes partial results (skip_prefix), with or without prefix rows
+    return (a.prefix > 0 || a.skip_prefix) ? launch_tma_pfx<T, D, BM, TN, true>(a, stream)
+                                           : launch_tma_pfx<T, D, BM, TN, false>(a, stream);
 }
 
 // tile_cols: 32, 64, or 0 = by grid size: 64-column tiles up to about eight CTAs per SM (measured:

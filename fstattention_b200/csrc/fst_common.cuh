@@ -90,11 +90,22 @@ struct AttnArgs {
     int part_slots;
 };
 
+// Prefix rows held in a page pool (a KV cache): pages of page_size rows, pool strides in elements.
+struct PagedArgs {
+    const void *k_pool, *v_pool;
+    const int32_t *block_table;          // [Z][table_stride] page numbers
+    const int32_t *prefix_lens;          // [Z] prefix rows of every batch element
+    int table_stride, page_size, n_pages;
+    int64_t stride_page, stride_row, stride_head;
+};
+
 cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);
 // returns cudaErrorNotSupported when no tensor-core instantiation fits
 cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream);
 // dense prefix on tcgen05: partial results of n_runs runs into slots first_slot..; D = 128 only
 cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream);
+cudaError_t launch_prefix_umma_paged(const AttnArgs &a, const PagedArgs &pg, int dtype, int n_runs, int first_slot,
+                                     cudaStream_t stream);
 // merge a.part_slots partial results into o (and lse)
 cudaError_t launch_combine(const AttnArgs &a, int dtype, cudaStream_t stream);
 

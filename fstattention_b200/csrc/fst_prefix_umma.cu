@@ -111,12 +111,18 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 struct PrefixArgs {
     int n_runs;          // runs of prefix rows (CTAs per query tile, head, batch element)
     int first_slot;      // partial-result slot of run 0 (slot 0 belongs to the tree kernel)
+    // paged prefix: K/V rows live in pages of page_size rows; block_table[z][i] is the page
+    // holding rows [i * page_size, (i + 1) * page_size) of batch element z, prefix_lens[z] its
+    // number of prefix rows (AttnArgs::prefix is then the largest of them)
+    const int32_t *block_table;
+    const int32_t *prefix_lens;
+    int table_stride, page_size, n_pages;
 };
 
 constexpr int PFX_SOFTMAX = 256;       // eight softmax warps: two groups of 128, one thread per query row each
 constexpr int PFX_THREADS = PFX_SOFTMAX + 64;   // + two issuing warps
 
-template <typename T>
+template <typename T, bool PAGED>
 __global__ void __launch_bounds__(PFX_THREADS, 1)
 prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
@@ -130,13 +136,15 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const int qt = blockIdx.x, h = blockIdx.y, hk = h / a.kv_group;   // query tile, head, K/V head
     const int z = blockIdx.z / pa.n_runs, run = blockIdx.z - z * pa.n_runs;
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int prefix = a.prefix, n_q = a.n_q;
+    const int n_q = a.n_q;
+    // prefix rows of my batch element (paged: every batch element has its own count)
+    const int prefix = PAGED ? min(__ldg(pa.prefix_lens + z), a.prefix) : a.prefix;
 
-    // my run of prefix rows, in whole tiles
-    const int tiles_total = (prefix + KN - 1) / KN, per = (tiles_total + pa.n_runs - 1) / pa.n_runs;
+    // my run of prefix rows, in whole tiles; the runs are cut from the largest prefix
+    const int tiles_total = (a.prefix + KN - 1) / KN, per = (tiles_total + pa.n_runs - 1) / pa.n_runs;
     const int t_lo = min(run * per, tiles_total), t_hi = min(t_lo + per, tiles_total);
-    const int nt = t_hi - t_lo;
     const int p_lo = t_lo * KN, p_end = min(prefix, t_hi * KN);
+    const int nt = p_end > p_lo ? (p_end - p_lo + KN - 1) / KN : 0;
 
     // barriers: Q, K[2], V[2] (TMA), S[2] (S product landed in its buffer), O[2] (O += P V done, per P buffer),
     // P[2] (all softmax threads are through with S(t) and have written P(t)).  Every barrier that is
@@ -147,17 +155,46 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
 
     // Thread 256 sets the barriers up and sends the first loads off before the CTA-wide sync, so
     // that they are under way while warp 9 allocates tensor memory.
-    auto load_k = [&](int t) {
-        const uint32_t bar = bar_k + (t & 1) * 8;
-        mbar_arrive_expect_tx(bar, TILE);
-        tma_load_4d(s_base + OFF_K + (t & 1) * TILE, &tm_k, 0, p_lo + t * KN, hk, z, bar);
-        tma_load_4d(s_base + OFF_K + (t & 1) * TILE + HALF, &tm_k, 64, p_lo + t * KN, hk, z, bar);
+    // Paged: a tile is KN / page_size pages, one TMA box each; the page numbers of a tile are read
+    // (fetch_pages) a tile before the boxes are requested, so their latency is off the path.
+    // Pages past the end of my batch element's prefix repeat its last page: finite values under
+    // columns the softmax masks.
+    constexpr int MAXP = KN / 16;                         // pages per tile at the smallest page size
+    const int ps = PAGED ? pa.page_size : KN, npt = KN / ps;
+    const int32_t *table = PAGED ? pa.block_table + size_t(z) * pa.table_stride : nullptr;
+    const int last_page = PAGED ? max(prefix - 1, 0) / ps : 0;
+    auto fetch_pages = [&](int t, int (&ids)[MAXP]) {
+        if (!PAGED) return;
+        const int first = (p_lo + t * KN) / ps;
+#pragma unroll
+        for (int j = 0; j < MAXP; ++j) {
+            ids[j] = 0;
+            if (j < npt) {
+                ids[j] = __ldg(table + min(first + j, last_page));
+                if (unsigned(ids[j]) >= unsigned(pa.n_pages)) report(a.status, FST_DEV_INDEX_RANGE, z, first + j);
+            }
+        }
     };
-    auto load_v = [&](int t) {
-        const uint32_t bar = bar_v + (t & 1) * 8;
+    auto load_tile = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int t, const int (&ids)[MAXP]) {
         mbar_arrive_expect_tx(bar, TILE);
-        tma_load_4d(s_base + OFF_V + (t & 1) * TILE, &tm_v, 0, p_lo + t * KN, hk, z, bar);
-        tma_load_4d(s_base + OFF_V + (t & 1) * TILE + HALF, &tm_v, 64, p_lo + t * KN, hk, z, bar);
+        if (PAGED) {
+#pragma unroll
+            for (int j = 0; j < MAXP; ++j) {
+                if (j < npt) {
+                    tma_load_4d(dst + j * ps * 128, map, 0, 0, hk, ids[j], bar);
+                    tma_load_4d(dst + j * ps * 128 + HALF, map, 64, 0, hk, ids[j], bar);
+                }
+            }
+        } else {
+            tma_load_4d(dst, map, 0, p_lo + t * KN, hk, z, bar);
+            tma_load_4d(dst + HALF, map, 64, p_lo + t * KN, hk, z, bar);
+        }
+    };
+    auto load_k = [&](int t, const int (&ids)[MAXP]) {
+        load_tile(s_base + OFF_K + (t & 1) * TILE, &tm_k, bar_k + (t & 1) * 8, t, ids);
+    };
+    auto load_v = [&](int t, const int (&ids)[MAXP]) {
+        load_tile(s_base + OFF_V + (t & 1) * TILE, &tm_v, bar_v + (t & 1) * 8, t, ids);
     };
     if (tid == PFX_SOFTMAX) {
         mbar_init(bar_q, 1);
@@ -173,11 +210,14 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
             mbar_arrive_expect_tx(bar_q, TILE);
             tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
             tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
-            load_k(0);
-            load_v(0);
+            int ids[MAXP];
+            fetch_pages(0, ids);
+            load_k(0, ids);
+            load_v(0, ids);
             if (nt > 1) {
-                load_k(1);
-                load_v(1);
+                fetch_pages(1, ids);
+                load_k(1, ids);
+                load_v(1, ids);
             }
         }
     }
@@ -199,6 +239,8 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         if (tid == PFX_SOFTMAX && nt > 0) {
             // descriptors of the tiles' first 16-wide step; a step further on adds its byte offset / 16
             const uint64_t dq = smem_desc(s_base + OFF_Q, 16), dk = smem_desc(s_base + OFF_K, 16);
+            int ids[MAXP];                                // pages of the tile to be requested next
+            if (nt > 2) fetch_pages(2, ids);
             alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
 #pragma unroll 1
             for (int t = 0; t < nt && alive; ++t) {       // S(t) = Q K(t)^T into S buffer t & 1
@@ -217,11 +259,14 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
                 mma_commit(bar_s + st * 8);
                 if (t + 2 < nt) {                         // K stage st is free as soon as S(t) has been formed
                     alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                    if (alive) load_k(t + 2);
+                    if (alive) load_k(t + 2, ids);
+                    if (t + 3 < nt) fetch_pages(t + 3, ids);
                 }
             }
         } else if (tid == PFX_SOFTMAX + 32 && nt > 0) {
             const uint64_t dp = smem_desc(s_base + OFF_P, 16), dv = smem_desc(s_base + OFF_V, HALF);
+            int ids[MAXP];
+            if (nt > 2) fetch_pages(2, ids);
 #pragma unroll 1
             for (int t = 0; t < nt && alive; ++t) {       // O_g += P(t) V(t), g = t & 1
                 const int st = t & 1;
@@ -238,7 +283,8 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
                 mma_commit(bar_o + st * 8);
                 if (t + 2 < nt) {                         // V stage st is free once that product has read it
                     alive = mbar_wait(bar_o + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                    if (alive) load_v(t + 2);
+                    if (alive) load_v(t + 2, ids);
+                    if (t + 3 < nt) fetch_pages(t + 3, ids);
                 }
             }
         }
@@ -433,35 +479,76 @@ static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T>
-static cudaError_t launch_prefix_t(const AttnArgs &a, int n_runs, int first_slot, cudaStream_t stream) {
+// rank-4 map over a page pool (columns, rows of a page, K/V heads, pages) with 64-column x page boxes
+static bool make_map_pool(CUtensorMap *map, const void *base, bool bf16, const PagedArgs &pg, int H_kv,
+                          const void *pool) {
+    (void)base;
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[4] = {cuuint64_t(umma::D), cuuint64_t(pg.page_size), cuuint64_t(H_kv), cuuint64_t(pg.n_pages)};
+    const cuuint64_t strides[3] = {cuuint64_t(pg.stride_row) * 2, cuuint64_t(pg.stride_head) * 2,
+                                   cuuint64_t(pg.stride_page) * 2};
+    const cuuint32_t box[4] = {64, cuuint32_t(pg.page_size), 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+              const_cast<void *>(pool), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, bool PAGED>
+static cudaError_t launch_prefix_t(const AttnArgs &a, const PagedArgs *pg, int n_runs, int first_slot,
+                                   cudaStream_t stream) {
     constexpr bool bf16 = !std::is_same<T, __half>::value;
     alignas(64) CUtensorMap tq, tk, tv;
-    if (!make_map_rows128(&tq, a.q, bf16, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
-        !make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-        !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z))
+    if (!make_map_rows128(&tq, a.q, bf16, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z)) return cudaErrorNotSupported;
+    if (PAGED) {
+        if (!make_map_pool(&tk, nullptr, bf16, *pg, a.H / a.kv_group, pg->k_pool) ||
+            !make_map_pool(&tv, nullptr, bf16, *pg, a.H / a.kv_group, pg->v_pool))
+            return cudaErrorNotSupported;
+    } else if (!make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+               !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z)) {
         return cudaErrorNotSupported;
+    }
     static bool configured_on[kMaxDevices] = {};
     const int slot = current_device_slot();
     if (slot < 0) return cudaErrorInvalidDevice;
     if (!configured_on[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              umma::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured_on[slot] = true;
     }
     if ((long long)a.Z * n_runs > 65535) return cudaErrorInvalidValue;
-    PrefixArgs pa{n_runs, first_slot};
+    PrefixArgs pa{n_runs, first_slot, nullptr, nullptr, 0, 0, 0};
+    if (PAGED) {
+        pa.block_table = pg->block_table;
+        pa.prefix_lens = pg->prefix_lens;
+        pa.table_stride = pg->table_stride;
+        pa.page_size = pg->page_size;
+        pa.n_pages = pg->n_pages;
+    }
     dim3 grid((a.n_q + umma::QM - 1) / umma::QM, a.H, a.Z * n_runs);
-    prefix_umma_kernel<T><<<grid, PFX_THREADS, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
+    prefix_umma_kernel<T, PAGED><<<grid, PFX_THREADS, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
     return cudaGetLastError();
 }
 
 // Partial results of the prefix, split into n_runs runs, into slots first_slot .. first_slot+n_runs-1.
 cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream) {
     if (a.D != umma::D || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
-    if (dtype == FST_F16) return launch_prefix_t<__half>(a, n_runs, first_slot, stream);
-    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16>(a, n_runs, first_slot, stream);
+    if (dtype == FST_F16) return launch_prefix_t<__half, false>(a, nullptr, n_runs, first_slot, stream);
+    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16, false>(a, nullptr, n_runs, first_slot, stream);
+    return cudaErrorNotSupported;
+}
+
+// The same with the prefix rows in a page pool; a.k / a.v are not read.
+cudaError_t launch_prefix_umma_paged(const AttnArgs &a, const PagedArgs &pg, int dtype, int n_runs, int first_slot,
+                                     cudaStream_t stream) {
+    if (a.D != umma::D || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
+    if (pg.page_size != 16 && pg.page_size != 32 && pg.page_size != 64 && pg.page_size != 128)
+        return cudaErrorNotSupported;
+    if (dtype == FST_F16) return launch_prefix_t<__half, true>(a, &pg, n_runs, first_slot, stream);
+    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16, true>(a, &pg, n_runs, first_slot, stream);
     return cudaErrorNotSupported;
 }
 

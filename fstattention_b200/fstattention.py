@@ -188,3 +188,74 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 ws.data_ptr(), ws_bytes, status.data_ptr(), stream)
             _lib.check(rc, "fst_attention_fwd_ref")
     return (o, lse) if return_lse else o
+
+
+def fst_attention_paged(q, k_tree, v_tree, meta: TreeMetadata, k_pool, v_pool, block_table, prefix_lens,
+                        sm_scale, *, max_prefix: Optional[int] = None, pool_layout: str = "NHD",
+                        kv_splits: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                        return_lse: bool = False):
+    """Tree attention behind a prefix held in a paged KV cache (head_dim 128, fp16 / bf16).
+
+    ``q`` is ``[Z, H, N, D]``; ``k_tree``, ``v_tree`` are the tree nodes' own K/V rows,
+    ``[Z, H_kv, N, D]``.  The prefix of batch element ``z`` is rows ``[0, prefix_lens[z])`` of
+    the sequence whose pages ``block_table[z]`` lists (int32, on the GPU, as is ``prefix_lens``):
+    row ``r`` lives in page ``block_table[z, r // page_size]``.  The pools are
+    ``[n_pages, page_size, H_kv, D]`` (``pool_layout="NHD"``) or ``[n_pages, H_kv, page_size, D]``
+    (``"HND"``), page_size 16, 32, 64 or 128.  ``max_prefix`` (default: the largest entry of
+    ``prefix_lens``, which costs a device synchronisation) sizes the grid.  ``meta`` is the
+    ``TreeMetadata`` of the tree (``build_tree_metadata``)."""
+    if not isinstance(meta, TreeMetadata):
+        raise TypeError("meta must be a TreeMetadata (build_tree_metadata)")
+    if not all(t.is_cuda for t in (q, k_tree, v_tree, k_pool, v_pool, block_table, prefix_lens)):
+        raise RuntimeError("fst_attention_paged runs on CUDA tensors only; there is no CPU path")
+    if q.dtype not in (torch.float16, torch.bfloat16) or any(t.dtype != q.dtype for t in (k_tree, v_tree, k_pool, v_pool)):
+        raise TypeError("q, k_tree, v_tree and the pools must share one dtype out of float16, bfloat16")
+    Z, H, n_q, D = q.shape
+    H_kv = k_tree.shape[1]
+    if k_tree.shape != (Z, H_kv, n_q, D) or v_tree.shape != k_tree.shape or H_kv < 1 or H % H_kv:
+        raise ValueError("k_tree and v_tree must be [Z, H_kv, N, D] with H a multiple of H_kv")
+    if pool_layout not in ("NHD", "HND"):
+        raise ValueError("pool_layout must be 'NHD' or 'HND'")
+    row_dim, head_dim_ = (1, 2) if pool_layout == "NHD" else (2, 1)
+    n_pages, page_size = k_pool.shape[0], k_pool.shape[row_dim]
+    if k_pool.dim() != 4 or v_pool.shape != k_pool.shape or k_pool.shape[head_dim_] != H_kv or k_pool.shape[3] != D \
+            or k_pool.stride() != v_pool.stride() or k_pool.stride(3) != 1:
+        raise ValueError("pools must be two equally laid out [n_pages, page_size, H_kv, D] (or HND) tensors")
+    if block_table.dtype != torch.int32 or prefix_lens.dtype != torch.int32 or block_table.dim() != 2 \
+            or block_table.shape[0] != Z or prefix_lens.shape != (Z,) or not block_table.is_contiguous():
+        raise ValueError("block_table must be contiguous int32 [Z, pages], prefix_lens int32 [Z]")
+    if meta.n_trees not in (1, Z) or meta.n_blocks != -(-n_q // meta.block_m):
+        raise ValueError("metadata does not match q")
+    if max_prefix is None:
+        max_prefix = int(prefix_lens.max().item())
+    if max_prefix <= 0:                                   # no prefix anywhere: plain tree attention
+        return fst_attention(q, k_tree, v_tree, meta, sm_scale=sm_scale, out=out, return_lse=return_lse)
+    o = torch.empty_like(q) if out is None else out
+    if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
+        raise ValueError("out must match q")
+    lse = torch.empty((Z * H, n_q), device=q.device, dtype=torch.float32) if return_lse else None
+    lib = _lib.lib()
+    dev = q.device
+    if kv_splits is None:
+        sms = _SMS.get(dev)
+        if sms is None:
+            sms = _SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+        ctas = Z * H * -(-n_q // 128)
+        kv_splits = int(max(1, min(sms // max(ctas, 1), max_prefix // 256, 65535 // Z)))
+    status = _status_record(dev)
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, kv_splits))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        rc = lib.fst_attention_fwd_paged(
+            q.data_ptr(), k_tree.data_ptr(), v_tree.data_ptr(), o.data_ptr(),
+            lse.data_ptr() if lse is not None else None,
+            meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0,
+            k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+            prefix_lens.data_ptr(), int(max_prefix), page_size, n_pages,
+            k_pool.stride(0), k_pool.stride(row_dim), k_pool.stride(head_dim_),
+            Z, H, H_kv, n_q, D, *_strides(q), *_strides(k_tree), *_strides(v_tree), *_strides(o),
+            meta.block_m, meta.max_ancestors, float(sm_scale), _DTYPES[q.dtype], kv_splits,
+            ws.data_ptr(), ws_bytes, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "fst_attention_fwd_paged")
+    return (o, lse) if return_lse else o
+

@@ -195,6 +195,36 @@ int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, 
                           int32_t *status, void *stream);
 
 /*
+ * Tree attention behind a prefix that lives in a paged KV cache.  The reference keeps prefix and
+ * tree rows in one contiguous K/V tensor (fstattention.py:163, 207-212); a serving engine keeps
+ * the prompt in pages.  Here the tree nodes' K/V rows come as tensors of their own
+ * (k_tree, v_tree: [Z, H_kv, n_q, head_dim] by the given strides) and the prefix rows of batch
+ * element z are rows [0, prefix_lens[z]) of the sequence whose pages block_table[z][0..] lists:
+ * row r sits in page block_table[z * table_stride + r / page_size] at row r % page_size.
+ * k_pool / v_pool: element (page, row, head, d) at page * pool_stride_page + row * pool_stride_row
+ * + head * pool_stride_head + d (element strides, multiples of 8).  page_size 16, 32, 64 or 128;
+ * head_dim 128; fp16 / bf16.  max_prefix >= every prefix_lens[z] (it sizes the grid; lengths
+ * above it are cut).  The prefix goes to the tcgen05 kernel in kv_splits runs, the tree part to
+ * the tree kernel, partial results through `workspace`
+ * (fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits) bytes).  A page number
+ * outside [0, n_pages) reads as zeros and sets FST_DEV_INDEX_RANGE.  block_table and prefix_lens
+ * are device pointers.
+ */
+int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tree, void *o, float *lse,
+                            const void *packed, size_t meta_tree_stride,
+                            const void *k_pool, const void *v_pool,
+                            const int32_t *block_table, int table_stride,
+                            const int32_t *prefix_lens, int max_prefix, int page_size, int n_pages,
+                            int64_t pool_stride_page, int64_t pool_stride_row, int64_t pool_stride_head,
+                            int Z, int H, int H_kv, int n_q, int head_dim,
+                            int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                            int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                            int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                            int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                            int block_m, int max_ancestors, float sm_scale, int dtype, int kv_splits,
+                            void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
  * The same with reference-format metadata, i.e. exactly the arguments of the reference's
  * fst_attention(q, k, v, ancestor_idx, ancestor_mask, leaf_idx, sm_scale, BLOCK_M,
  * MAX_ANCESTORS) (fstattention.py:153).  Index tensors hold absolute K/V rows

@@ -378,6 +378,73 @@ def test_grouped_query_attention(fst, prefix):
     assert fst.last_status() == 0
 
 
+def _scatter_into_pages(k, v, prefix_lens, page_size, layout, seed):
+    """Put the prefix rows of [Z, H_kv, P_max + N, D] tensors into a shuffled page pool."""
+    Z, H_kv, _, D = k.shape
+    pages_per_seq = [-(-p // page_size) for p in prefix_lens]
+    n_pages = sum(pages_per_seq) + 3                      # a few pages nobody owns
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    shape = (n_pages, page_size, H_kv, D) if layout == "NHD" else (n_pages, H_kv, page_size, D)
+    k_pool = torch.randn(shape, generator=g).to(k.dtype)  # unowned rows hold finite junk
+    v_pool = torch.randn(shape, generator=g).to(k.dtype)
+    table = torch.full((Z, max(pages_per_seq) + 1), -7, dtype=torch.int32)   # entries past a sequence are junk
+    nxt = 0
+    for z in range(Z):
+        for i in range(pages_per_seq[z]):
+            pid = perm[nxt]; nxt += 1
+            table[z, i] = pid
+            rows = min(page_size, prefix_lens[z] - i * page_size)
+            src = slice(i * page_size, i * page_size + rows)
+            if layout == "NHD":
+                k_pool[pid, :rows] = k[z, :, src].transpose(0, 1)
+                v_pool[pid, :rows] = v[z, :, src].transpose(0, 1)
+            else:
+                k_pool[pid, :, :rows] = k[z, :, src]
+                v_pool[pid, :, :rows] = v[z, :, src]
+    return k_pool, v_pool, table
+
+
+@pytest.mark.parametrize("page_size,layout,dtype", [(16, "NHD", torch.float16), (64, "HND", torch.float16),
+                                                   (128, "NHD", torch.bfloat16), (32, "NHD", torch.float16)])
+def test_paged_prefix(fst, page_size, layout, dtype):
+    """Prefix rows in a shuffled page pool with a different length per batch element, tree rows
+    in their own tensors, grouped K/V heads: equal to attention over the same rows laid out
+    contiguously (oracle), and to the contiguous tcgen05 path where the lengths allow."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, H_kv, D = 256, 4, 2, 128
+    prefix_lens = [700, 129, 1024]
+    Z, p_max = len(prefix_lens), max(prefix_lens)
+    q, _, _ = make_qkv(Z, H, n, n, D, dtype, seed=71)
+    _, k, v = make_qkv(Z, H_kv, n, p_max + n, D, dtype, seed=72)     # rows [0, P_z) prefix, [p_max, p_max + n) tree
+    scale = D ** -0.5
+    meta = fst.build_tree_metadata(par, 64, 64)
+    k_pool, v_pool, table = _scatter_into_pages(k, v, prefix_lens, page_size, layout, seed=73)
+    k_tree, v_tree = k[:, :, p_max:].contiguous(), v[:, :, p_max:].contiguous()
+    lens = torch.tensor(prefix_lens, dtype=torch.int32)
+    tol = TOL_F16 if dtype == torch.float16 else TOL_BF16
+    for splits in (1, 3, None):
+        out, lse = fst.fst_attention_paged(q.cuda(), k_tree.cuda(), v_tree.cuda(), meta, k_pool.cuda(), v_pool.cuda(),
+                                           table.cuda(), lens.cuda(), scale, pool_layout=layout, kv_splits=splits,
+                                           return_lse=True)
+        assert torch.isfinite(out).all()
+        for z, pz in enumerate(prefix_lens):
+            kz = torch.cat([k[z:z + 1, :, :pz], k[z:z + 1, :, p_max:]], dim=2).repeat_interleave(H // H_kv, dim=1)
+            vz = torch.cat([v[z:z + 1, :, :pz], v[z:z + 1, :, p_max:]], dim=2).repeat_interleave(H // H_kv, dim=1)
+            exact = oracle_attention(q[z:z + 1], kz, vz, par, scale, prefix=pz, compute_dtype=torch.float32)
+            assert maxabs(out[z:z + 1].cpu(), exact) <= tol, (splits, z, maxabs(out[z:z + 1].cpu(), exact))
+    # the longest sequence against the contiguous path with the same number of runs: same tiles, same bits
+    z = prefix_lens.index(p_max)
+    cont = fst.fst_attention(q[z:z + 1].cuda(), k[z:z + 1].cuda(), v[z:z + 1].cuda(), meta, sm_scale=scale,
+                             kernel="tma_umma", kv_splits=3)
+    paged = fst.fst_attention_paged(q[z:z + 1].cuda(), k_tree[z:z + 1].cuda(), v_tree[z:z + 1].cuda(), meta,
+                                    k_pool.cuda(), v_pool.cuda(), table[z:z + 1].contiguous().cuda(), lens[z:z + 1].cuda(),
+                                    scale, pool_layout=layout, kv_splits=3)
+    assert torch.equal(cont, paged)
+    assert fst.last_status() == 0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
