@@ -15,12 +15,15 @@
 // Ten warps.  Warps 0-3 and 4-7 are two softmax groups; group g takes the tiles with t & 1 == g
 // and keeps its own reference point, row sums, P buffer and accumulator O_g, so the groups never
 // wait for one another and one group's barrier waits and tensor-memory latencies hide behind the
-// other's exponentials.  Lane 0 of warp 8 loads K and issues S(t); lane 0 of warp 9 loads V and
+// other's exponentials.  Warp 8 loads K and its lane 0 issues S(t); warp 9 loads V and its lane 0
 // issues O_g += P V.  All hand-offs are mbarriers (TMA completion, tcgen05.commit, or arrivals by
 // the 128 threads of a group); every barrier indexed by t & 1 completes once per two tiles, so a
 // waiter can never fall two phases behind.  At the end the groups' results are merged through
 // shared memory and written as one partial result per run (normalised rows in fp32 plus base-2
 // log-sum-exp) in the layout the tree kernel writes; combine_splits_kernel merges the runs.
+//
+// PAGED = true reads the prefix rows from a page pool through a block table (a KV cache): a
+// tile is 128 / page_size pages and lane j of the loading warp requests page j.
 //
 // Every wait is bounded in time (mbar_wait): on expiry the kernel records FST_DEV_TIMEOUT, stops
 // issuing, frees its tensor memory and returns.
@@ -153,71 +156,64 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
                    bar_o = bar_q + 56, bar_p = bar_q + 72;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + OFF_BAR + 112);
 
-    // Thread 256 sets the barriers up and sends the first loads off before the CTA-wide sync, so
-    // that they are under way while warp 9 allocates tensor memory.
-    // Paged: a tile is KN / page_size pages, one TMA box each; the page numbers of a tile are read
-    // (fetch_pages) a tile before the boxes are requested, so their latency is off the path.
-    // Pages past the end of my batch element's prefix repeat its last page: finite values under
-    // columns the softmax masks.
-    constexpr int MAXP = KN / 16;                         // pages per tile at the smallest page size
+    // Loads are issued by whole warps (8: K, 9: V).  Contiguous prefix: lane 0 requests the two
+    // boxes of a tile.  Paged: a tile is KN / page_size pages, one pair of boxes each, and lane j
+    // takes page j - it reads that page's number from the block table (my_page) a tile before
+    // it requests the boxes, so the table's latency is off the path, and a single thread is
+    // not left to issue sixteen copies one after the other.  Pages past the end of my batch
+    // element's prefix repeat its last page: finite values under columns the softmax masks.
+    const int lane = tid & 31;
     const int ps = PAGED ? pa.page_size : KN, npt = KN / ps;
     const int32_t *table = PAGED ? pa.block_table + size_t(z) * pa.table_stride : nullptr;
     const int last_page = PAGED ? max(prefix - 1, 0) / ps : 0;
-    auto fetch_pages = [&](int t, int (&ids)[MAXP]) {
-        if (!PAGED) return;
-        const int first = (p_lo + t * KN) / ps;
-#pragma unroll
-        for (int j = 0; j < MAXP; ++j) {
-            ids[j] = 0;
-            if (j < npt) {
-                ids[j] = __ldg(table + min(first + j, last_page));
-                if (unsigned(ids[j]) >= unsigned(pa.n_pages)) report(a.status, FST_DEV_INDEX_RANGE, z, first + j);
-            }
-        }
+    auto my_page = [&](int t) -> int {
+        if (!PAGED || lane >= npt) return 0;
+        return __ldg(table + min((p_lo + t * KN) / ps + lane, last_page));
     };
-    auto load_tile = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int t, const int (&ids)[MAXP]) {
-        mbar_arrive_expect_tx(bar, TILE);
+    auto warp_load = [&](uint32_t dst, const CUtensorMap *map, uint32_t bar, int t, int page) {
+        if (lane == 0) mbar_arrive_expect_tx(bar, TILE);
+        if (PAGED) __syncwarp();                          // (contiguous: only lane 0 ever comes here)
         if (PAGED) {
-#pragma unroll
-            for (int j = 0; j < MAXP; ++j) {
-                if (j < npt) {
-                    tma_load_4d(dst + j * ps * 128, map, 0, 0, hk, ids[j], bar);
-                    tma_load_4d(dst + j * ps * 128 + HALF, map, 64, 0, hk, ids[j], bar);
-                }
+            if (lane < npt) {
+                if (unsigned(page) >= unsigned(pa.n_pages))       // the boxes then read as zeros
+                    report(a.status, FST_DEV_INDEX_RANGE, z, (p_lo + t * KN) / ps + lane);
+                tma_load_4d(dst + lane * ps * 128, map, 0, 0, hk, page, bar);
+                tma_load_4d(dst + lane * ps * 128 + HALF, map, 64, 0, hk, page, bar);
             }
-        } else {
+        } else if (lane == 0) {
             tma_load_4d(dst, map, 0, p_lo + t * KN, hk, z, bar);
             tma_load_4d(dst + HALF, map, 64, p_lo + t * KN, hk, z, bar);
         }
     };
-    auto load_k = [&](int t, const int (&ids)[MAXP]) {
-        load_tile(s_base + OFF_K + (t & 1) * TILE, &tm_k, bar_k + (t & 1) * 8, t, ids);
-    };
-    auto load_v = [&](int t, const int (&ids)[MAXP]) {
-        load_tile(s_base + OFF_V + (t & 1) * TILE, &tm_v, bar_v + (t & 1) * 8, t, ids);
-    };
-    if (tid == PFX_SOFTMAX) {
-        mbar_init(bar_q, 1);
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(bar_k + i * 8, 1);
-            mbar_init(bar_v + i * 8, 1);
-            mbar_init(bar_s + i * 8, 1);
-            mbar_init(bar_o + i * 8, 1);
-            mbar_init(bar_p + i * 8, PFX_SOFTMAX / 2);
+    auto load_k = [&](int t, int page) { warp_load(s_base + OFF_K + (t & 1) * TILE, &tm_k, bar_k + (t & 1) * 8, t, page); };
+    auto load_v = [&](int t, int page) { warp_load(s_base + OFF_V + (t & 1) * TILE, &tm_v, bar_v + (t & 1) * 8, t, page); };
+    // Warp 8 sets the barriers up and sends the first loads off before the CTA-wide sync, so that
+    // they are under way while warp 9 allocates tensor memory.
+    if (warp == 8) {
+        if (lane == 0) {
+            mbar_init(bar_q, 1);
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(bar_k + i * 8, 1);
+                mbar_init(bar_v + i * 8, 1);
+                mbar_init(bar_s + i * 8, 1);
+                mbar_init(bar_o + i * 8, 1);
+                mbar_init(bar_p + i * 8, PFX_SOFTMAX / 2);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        if (nt > 0) {
-            mbar_arrive_expect_tx(bar_q, TILE);
-            tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
-            tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
-            int ids[MAXP];
-            fetch_pages(0, ids);
-            load_k(0, ids);
-            load_v(0, ids);
+        __syncwarp();
+        if (nt > 0 && (PAGED || lane == 0)) {
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar_q, TILE);
+                tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
+                tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
+            }
+            const int page0 = my_page(0), page1 = nt > 1 ? my_page(1) : 0;
+            load_k(0, page0);
+            load_v(0, page0);
             if (nt > 1) {
-                fetch_pages(1, ids);
-                load_k(1, ids);
-                load_v(1, ids);
+                load_k(1, page1);
+                load_v(1, page1);
             }
         }
     }
@@ -233,58 +229,70 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;   // S(t) at tmem_s0 + (t & 1) * 128, O_g at tmem_o + g * 128
 
     if (warp >= 8) {
-        // ================ two issuing threads: warp 8 for K and S = Q K^T, warp 9 for V and O += P V ================
+        // ====== two issuing warps: 8 loads K and issues S = Q K^T, 9 loads V and issues O += P V ======
+        // Lane 0 waits and issues the products; the whole warp takes part in the loads.
         const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
         bool alive = true;
-        if (tid == PFX_SOFTMAX && nt > 0) {
+        if (warp == 8 && nt > 0 && (PAGED || lane == 0)) {     // contiguous: lane 0 alone
             // descriptors of the tiles' first 16-wide step; a step further on adds its byte offset / 16
             const uint64_t dq = smem_desc(s_base + OFF_Q, 16), dk = smem_desc(s_base + OFF_K, 16);
-            int ids[MAXP];                                // pages of the tile to be requested next
-            if (nt > 2) fetch_pages(2, ids);
-            alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
+            int page = nt > 2 ? my_page(2) : 0;           // my page of the tile to be requested next
+            if (lane == 0) alive = mbar_wait(bar_q, 0, a.status, qt) && alive;
 #pragma unroll 1
-            for (int t = 0; t < nt && alive; ++t) {       // S(t) = Q K(t)^T into S buffer t & 1
+            for (int t = 0; t < nt; ++t) {                // S(t) = Q K(t)^T into S buffer t & 1
                 const int st = t & 1;
-                // the buffer is free when the softmax warps are through with tile t-2
-                if (t > 1) alive = mbar_wait(bar_p + st * 8, ((t >> 1) - 1) & 1, a.status, qt) && alive;
-                alive = mbar_wait(bar_k + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                if (!alive) break;
-                umma::fence_after_sync();
-                const uint64_t dks = dk + uint64_t(st * (TILE >> 4));
+                if (lane == 0 && alive) {
+                    // the buffer is free when the softmax warps are through with tile t-2
+                    if (t > 1) alive = mbar_wait(bar_p + st * 8, ((t >> 1) - 1) & 1, a.status, qt) && alive;
+                    alive = mbar_wait(bar_k + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                    if (alive) {
+                        umma::fence_after_sync();
+                        const uint64_t dks = dk + uint64_t(st * (TILE >> 4));
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t koff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
-                    mma_f16(tmem_s0 + st * 128, dq + koff, dks + koff, idesc_s, ks > 0);
+                        for (int ks = 0; ks < D / 16; ++ks) {
+                            const uint64_t koff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
+                            mma_f16(tmem_s0 + st * 128, dq + koff, dks + koff, idesc_s, ks > 0);
+                        }
+                        mma_commit(bar_s + st * 8);
+                        // K stage st is free as soon as S(t) has been formed
+                        if (t + 2 < nt) alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                    }
                 }
-                mma_commit(bar_s + st * 8);
-                if (t + 2 < nt) {                         // K stage st is free as soon as S(t) has been formed
-                    alive = mbar_wait(bar_s + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                    if (alive) load_k(t + 2, ids);
-                    if (t + 3 < nt) fetch_pages(t + 3, ids);
+                if (PAGED) alive = __shfl_sync(0xffffffffu, alive, 0);
+                if (!alive) break;
+                if (t + 2 < nt) {
+                    load_k(t + 2, page);
+                    if (t + 3 < nt) page = my_page(t + 3);
                 }
             }
-        } else if (tid == PFX_SOFTMAX + 32 && nt > 0) {
+        } else if (warp == 9 && nt > 0 && (PAGED || lane == 0)) {
             const uint64_t dp = smem_desc(s_base + OFF_P, 16), dv = smem_desc(s_base + OFF_V, HALF);
-            int ids[MAXP];
-            if (nt > 2) fetch_pages(2, ids);
+            int page = nt > 2 ? my_page(2) : 0;
 #pragma unroll 1
-            for (int t = 0; t < nt && alive; ++t) {       // O_g += P(t) V(t), g = t & 1
+            for (int t = 0; t < nt; ++t) {                // O_g += P(t) V(t), g = t & 1
                 const int st = t & 1;
-                alive = mbar_wait(bar_p + st * 8, (t >> 1) & 1, a.status, qt) && alive;   // P(t) is in shared memory
-                alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                if (!alive) break;
-                umma::fence_after_sync();
-                const uint64_t dps = dp + uint64_t(st * (TILE >> 4)), dvs = dv + uint64_t(st * (TILE >> 4));
+                if (lane == 0 && alive) {
+                    alive = mbar_wait(bar_p + st * 8, (t >> 1) & 1, a.status, qt) && alive;   // P(t) is in shared memory
+                    alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                    if (alive) {
+                        umma::fence_after_sync();
+                        const uint64_t dps = dp + uint64_t(st * (TILE >> 4)), dvs = dv + uint64_t(st * (TILE >> 4));
 #pragma unroll
-                for (int ks = 0; ks < KN / 16; ++ks) {    // 16 prefix rows per step
-                    const uint64_t aoff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
-                    mma_f16(tmem_o + st * 128, dps + aoff, dvs + uint64_t((ks * 16 * 128) >> 4), idesc_pv, t > 1 || ks > 0);
+                        for (int ks = 0; ks < KN / 16; ++ks) {    // 16 prefix rows per step
+                            const uint64_t aoff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
+                            mma_f16(tmem_o + st * 128, dps + aoff, dvs + uint64_t((ks * 16 * 128) >> 4), idesc_pv,
+                                    t > 1 || ks > 0);
+                        }
+                        mma_commit(bar_o + st * 8);
+                        // V stage st is free once that product has read it
+                        if (t + 2 < nt) alive = mbar_wait(bar_o + st * 8, (t >> 1) & 1, a.status, qt) && alive;
+                    }
                 }
-                mma_commit(bar_o + st * 8);
-                if (t + 2 < nt) {                         // V stage st is free once that product has read it
-                    alive = mbar_wait(bar_o + st * 8, (t >> 1) & 1, a.status, qt) && alive;
-                    if (alive) load_v(t + 2, ids);
-                    if (t + 3 < nt) fetch_pages(t + 3, ids);
+                if (PAGED) alive = __shfl_sync(0xffffffffu, alive, 0);
+                if (!alive) break;
+                if (t + 2 < nt) {
+                    load_v(t + 2, page);
+                    if (t + 3 < nt) page = my_page(t + 3);
                 }
             }
         }
@@ -425,7 +433,6 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         }
         asm volatile("bar.sync 1, 256;\n" ::: "memory");
         const size_t slot = size_t(pa.first_slot + run);
-        const int lane = tid & 31;
         constexpr int RPW = QM / (PFX_SOFTMAX / 32);      // 16 rows per warp: rows warp * 16 ..
         // lanes 0..15 work out the two groups' weights for one row each; they are handed round by shuffle
         float f0 = 0.f, f1 = 0.f;
