@@ -11,7 +11,9 @@ Printed JSON (one line, rank 0):
   value        gathered-KV GB/s over the whole step (inputs resident in HBM, step replayed as a
                CUDA graph), summed over ranks; ms_per_step and us_per_call give the latency view
   e2e          the same metric through the public Python API / C ABI with HOST buffers: every
-               step copies parent, Q, K, V from pinned host memory and copies O back
+               step copies parent, Q, K, V from pinned host memory and copies O back; copy-in,
+               attention and copy-out of consecutive calls overlap on three streams (the figure
+               is bound by the host-to-device link: three tensors in for one out)
   roofline     attention kernel: algorithmic gathered-KV bytes per launch / average launch
                duration (CUDA events around a graph of LAYERS back-to-back launches) against the
                measured HBM copy bandwidth
@@ -319,21 +321,55 @@ def run_ours(args, rank, world):
     e2e = None
     if not args.no_e2e:
         e2e_layers = min(L, 16)
-        host_in = [tuple(t.cpu().pin_memory() for t in trip) for trip in layers[:e2e_layers]]
+        # without a prefix q, k and v have one shape: the host keeps them as views of one pinned
+        # buffer per call (a fused qkv), which then crosses PCIe in a single copy
+        fused = w.prefix == 0
+        if fused:
+            host_in = [torch.stack([t.cpu() for t in trip]).pin_memory() for trip in layers[:e2e_layers]]
+        else:
+            host_in = [tuple(t.cpu().pin_memory() for t in trip) for trip in layers[:e2e_layers]]
         host_out = [torch.empty((T, H, N, D), dtype=dtype).pin_memory() for _ in range(e2e_layers)]
         host_parent = parent.cpu().pin_memory()
-        dq, dk, dv = (torch.empty_like(t) for t in layers[0])    # k, v carry the prefix rows
+        # Three streams, two device slots: the copy-in of call i+1, the attention of call i and the
+        # copy-out of call i-1 overlap (PCIe is full duplex and the copy engines are separate), as
+        # a host that feeds the library from its own buffers would arrange it.
+        if fused:
+            slots = [torch.empty((3,) + tuple(layers[0][0].shape), dtype=dtype, device=dev) for _ in range(2)]
+        else:
+            slots = [tuple(torch.empty_like(t) for t in layers[0]) for _ in range(2)]    # k, v carry the prefix rows
+        slot_out = [torch.empty_like(outs[0]) for _ in range(2)]
         dpar = torch.empty_like(parent)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        s_cmp = torch.cuda.current_stream(dev)
+        ev_in = [torch.cuda.Event() for _ in range(2)]      # inputs of the slot have arrived
+        ev_cmp = [torch.cuda.Event() for _ in range(2)]     # attention on the slot is done
+        ev_out = [torch.cuda.Event() for _ in range(2)]     # the slot's output has left
 
         def e2e_step():
             dpar.copy_(host_parent, non_blocking=True)
             fst.build_tree_metadata(dpar, w.block_m, w.max_ancestors, out=meta, check=False)
-            for (hq, hk, hv), ho, o in zip(host_in, host_out, outs):
-                dq.copy_(hq, non_blocking=True)
-                dk.copy_(hk, non_blocking=True)
-                dv.copy_(hv, non_blocking=True)
-                fst.fst_attention(dq, dk, dv, meta, sm_scale=w.sm_scale, out=o, kernel=args.kernel)
-                ho.copy_(o, non_blocking=True)
+            for i, (hin, ho) in enumerate(zip(host_in, host_out)):
+                sl = i & 1
+                dq, dk, dv = slots[sl]                      # (rows of the fused slot, or the three tensors)
+                with torch.cuda.stream(s_in):
+                    if i >= 2:
+                        s_in.wait_event(ev_cmp[sl])         # the slot's previous inputs have been used
+                    if fused:
+                        slots[sl].copy_(hin, non_blocking=True)
+                    else:
+                        dq.copy_(hin[0], non_blocking=True)
+                        dk.copy_(hin[1], non_blocking=True)
+                        dv.copy_(hin[2], non_blocking=True)
+                    ev_in[sl].record(s_in)
+                s_cmp.wait_event(ev_in[sl])
+                if i >= 2:
+                    s_cmp.wait_event(ev_out[sl])            # the slot's previous output has left
+                fst.fst_attention(dq, dk, dv, meta, sm_scale=w.sm_scale, out=slot_out[sl], kernel=args.kernel)
+                ev_cmp[sl].record(s_cmp)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_cmp[sl])
+                    ho.copy_(slot_out[sl], non_blocking=True)
+                    ev_out[sl].record(s_out)
             torch.cuda.synchronize()
 
         for _ in range(3):
@@ -355,7 +391,9 @@ def run_ours(args, rank, world):
                "h2d_bytes_per_step": e2e_layers * in_bytes + parent.numel() * 4,
                "d2h_bytes_per_step": e2e_layers * tensor_bytes,
                "ms_per_step": dt * 1e3, "calls_per_step": e2e_layers,
-               "us_per_call": dt * 1e6 / e2e_layers}
+               "us_per_call": dt * 1e6 / e2e_layers,
+               "overlap": "copy-in, attention and copy-out of consecutive calls on three streams, two device slots",
+               "inputs": "q, k, v are views of one pinned buffer per call, one copy" if fused else "q, k, v pinned separately, three copies per call"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
