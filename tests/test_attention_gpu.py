@@ -295,6 +295,26 @@ def test_prefix_split_over_ctas(fst, prefix, splits):
     assert fst.last_status() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_prefix_with_head_dim_64(fst, dtype):
+    """head_dim 64 has no tcgen05 prefix kernel: the tree kernel walks the prefix, alone or split
+    over CTAs, and the automatic choice must pick that without being asked."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D, prefix = 256, 3, 64, 900
+    q, k, v = make_qkv(2, H, n, prefix + n, D, dtype, seed=81)
+    scale = D ** -0.5
+    exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
+    meta = fst.build_tree_metadata(par, 64, 64)
+    tol = TOL_F16 if dtype == torch.float16 else TOL_BF16
+    for kern, splits in (("auto", None), ("auto", 4), ("tma_t32", 3), ("tma_t64", 1), ("mma", None), ("simt", None)):
+        out = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern, kv_splits=splits)
+        assert maxabs(out.cpu(), exact) <= tol, (kern, splits, maxabs(out.cpu(), exact))
+    with pytest.raises(RuntimeError):
+        fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel="tma_umma", kv_splits=2)
+    assert fst.last_status() == 0
+
+
 @pytest.mark.parametrize("prefix,runs,n,dtype", [(128, 1, 256, torch.float16), (129, 2, 200, torch.float16),
                                                   (700, 1, 256, torch.float16), (1111, 3, 130, torch.float16),
                                                   (1111, 2, 256, torch.bfloat16)])
