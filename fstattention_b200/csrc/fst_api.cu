@@ -233,10 +233,10 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
 
     // A shared prefix with a workspace: either the tcgen05 prefix kernel takes it in kv_splits runs
-    // while the tree kernel does the tree part (head_dim 128; chosen automatically from 256
+    // while the tree kernel does the tree part (head_dim 64 or 128; chosen automatically from 256
     // prefix rows on), or the tree kernel itself is launched kv_splits times over the prefix.
     const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA;
-    const bool want_umma = can_part && head_dim == 128 &&
+    const bool want_umma = can_part && (head_dim == 128 || head_dim == 64) &&
                            (choice == FST_KERNEL_TMA_UMMA || (automatic && a.prefix >= 256));
     if (choice == FST_KERNEL_TMA_UMMA && !want_umma) return FST_ERR_UNSUPPORTED;
     if (can_part && (want_umma || kv_splits > 1)) {
@@ -348,7 +348,7 @@ int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tre
         !workspace || Z <= 0 || H <= 0 || H_kv <= 0 || H % H_kv != 0 || n_q <= 0 || block_m <= 0 ||
         max_ancestors <= 0 || max_prefix <= 0 || n_pages <= 0 || kv_splits < 1 || table_stride <= 0)
         return FST_ERR_INVALID_ARG;
-    if (head_dim != 128 || !mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
+    if ((head_dim != 128 && head_dim != 64) || !mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return FST_ERR_UNSUPPORTED;
     if (H > 65535 || Z > 65535 || (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
     if ((long long)table_stride * page_size < max_prefix) return FST_ERR_INVALID_ARG;

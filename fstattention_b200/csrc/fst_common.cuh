@@ -102,7 +102,7 @@ struct PagedArgs {
 cudaError_t launch_attention_simt(const AttnArgs &a, int dtype, cudaStream_t stream);
 // returns cudaErrorNotSupported when no tensor-core instantiation fits
 cudaError_t launch_attention_mma(const AttnArgs &a, int dtype, int variant, cudaStream_t stream);
-// dense prefix on tcgen05: partial results of n_runs runs into slots first_slot..; D = 128 only
+// dense prefix on tcgen05: partial results of n_runs runs into slots first_slot..; D = 64 or 128
 cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream);
 cudaError_t launch_prefix_umma_paged(const AttnArgs &a, const PagedArgs &pg, int dtype, int n_runs, int first_slot,
                                      cudaStream_t stream);

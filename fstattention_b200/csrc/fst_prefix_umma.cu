@@ -4,13 +4,14 @@
 // every query row attends to every prefix row.  That is the one place on this path where the
 // tiles are large and dense, so it gets its own kernel: one CTA per (128 query rows, head,
 // batch element, run of prefix rows).  Per 128-row K/V tile t
-//     S(t) = Q K(t)^T       tcgen05.mma  M=128 N=128 K=16 x 8, both operands K-major in shared memory
+//     S(t) = Q K(t)^T       tcgen05.mma  M=128 N=128 K=16 x D/16, both operands K-major in shared memory
 //     P(t) = softmax part   one thread per query row (TMEM lane = row, so no shuffles): tcgen05.ld
 //                           of S, probabilities against a lazily moved reference point, P written
 //                           to shared memory in the 128-byte-swizzled K-major layout
 //     O_g += P(t) V(t)      tcgen05.mma  A = P, B = V (MN-major: rows of V are the K index)
 // Tensor memory holds two S buffers and two accumulators O_0, O_1 (4 x 128 columns).  K/V tiles
-// arrive by TMA (128-row x 64-column boxes, 128-byte swizzle) into two stages each.
+// arrive by TMA (128-row x 64-column boxes, 128-byte swizzle) into two stages each.  Head
+// dimension D is 64 or 128: one or two 64-column halves per Q / K / V tile.
 //
 // Ten warps.  Warps 0-3 and 4-7 are two softmax groups; group g takes the tiles with t & 1 == g
 // and keeps its own reference point, row sums, P buffer and accumulator O_g, so the groups never
@@ -34,17 +35,23 @@ namespace fst {
 
 namespace umma {
 
-constexpr int D = 128;                 // head dimension this kernel is built for
 constexpr int QM = 128;                // query rows per CTA (MMA M)
 constexpr int KN = 128;                // K/V rows per tile (MMA N of the first product)
 constexpr int HALF = QM * 128;         // bytes of one 64-column half of a 128-row tile
-constexpr int TILE = 2 * HALF;         // bytes of a 128 x 128 fp16 tile
-constexpr int OFF_Q = 0;
-constexpr int OFF_P = OFF_Q + TILE;
-constexpr int OFF_K = OFF_P + 2 * TILE;    // P is double buffered; K and V have two stages each
-constexpr int OFF_V = OFF_K + 2 * TILE;
-constexpr int OFF_BAR = OFF_V + 2 * TILE;
-constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;   // + barriers, TMEM address, 1 KB alignment slack
+constexpr int TILE_P = 2 * HALF;       // bytes of a P tile (128 x 128 fp16)
+
+// Shared-memory map for head dimension D (64 or 128): a Q / K / V tile is 128 rows of D columns,
+// D / 64 halves.  Q | P x 2 (double buffered) | K x 2 stages | V x 2 stages | barriers.
+template <int D>
+struct Geo {
+    static constexpr int TILE = (D / 64) * HALF;
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_P = OFF_Q + TILE;
+    static constexpr int OFF_K = OFF_P + 2 * TILE_P;
+    static constexpr int OFF_V = OFF_K + 2 * TILE;
+    static constexpr int OFF_BAR = OFF_V + 2 * TILE;
+    static constexpr int SMEM_BYTES = OFF_BAR + 128 + 1024;   // + barriers, TMEM address, 1 KB alignment slack
+};
 
 // shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1 KB apart
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
@@ -57,11 +64,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes)
     return d;
 }
 
-// instruction descriptor: f32 accumulate, M=128, N=128, A K-major, B K- or MN-major
-__device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major) {
+// instruction descriptor: f32 accumulate, M=128, N=n, A K-major, B K- or MN-major
+__device__ __forceinline__ uint32_t instr_desc(bool bf16, bool b_mn_major, int n) {
     const uint32_t fmt = bf16 ? 1u : 0u;
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(b_mn_major) << 16) |
-           (uint32_t(KN >> 3) << 17) | (uint32_t(QM >> 4) << 24);
+           (uint32_t(n >> 3) << 17) | (uint32_t(QM >> 4) << 24);
 }
 
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -125,13 +132,17 @@ struct PrefixArgs {
 constexpr int PFX_SOFTMAX = 256;       // eight softmax warps: two groups of 128, one thread per query row each
 constexpr int PFX_THREADS = PFX_SOFTMAX + 64;   // + two issuing warps
 
-template <typename T, bool PAGED>
+template <typename T, int D, bool PAGED>
 __global__ void __launch_bounds__(PFX_THREADS, 1)
 prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
     using namespace umma;
     using MT = MmaTraits<T>;
+    using G = Geo<D>;
     constexpr bool BF16 = !std::is_same<T, __half>::value;
+    constexpr int DH = D / 64;                            // 64-column halves of a Q / K / V tile
+    constexpr int TILE = G::TILE, OFF_Q = G::OFF_Q, OFF_P = G::OFF_P, OFF_K = G::OFF_K, OFF_V = G::OFF_V,
+                  OFF_BAR = G::OFF_BAR;
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -177,12 +188,13 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
             if (lane < npt) {
                 if (unsigned(page) >= unsigned(pa.n_pages))       // the boxes then read as zeros
                     report(a.status, FST_DEV_INDEX_RANGE, z, (p_lo + t * KN) / ps + lane);
-                tma_load_4d(dst + lane * ps * 128, map, 0, 0, hk, page, bar);
-                tma_load_4d(dst + lane * ps * 128 + HALF, map, 64, 0, hk, page, bar);
+#pragma unroll
+                for (int hf = 0; hf < DH; ++hf)
+                    tma_load_4d(dst + lane * ps * 128 + hf * HALF, map, hf * 64, 0, hk, page, bar);
             }
         } else if (lane == 0) {
-            tma_load_4d(dst, map, 0, p_lo + t * KN, hk, z, bar);
-            tma_load_4d(dst + HALF, map, 64, p_lo + t * KN, hk, z, bar);
+#pragma unroll
+            for (int hf = 0; hf < DH; ++hf) tma_load_4d(dst + hf * HALF, map, hf * 64, p_lo + t * KN, hk, z, bar);
         }
     };
     auto load_k = [&](int t, int page) { warp_load(s_base + OFF_K + (t & 1) * TILE, &tm_k, bar_k + (t & 1) * 8, t, page); };
@@ -205,8 +217,9 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         if (nt > 0 && (PAGED || lane == 0)) {
             if (lane == 0) {
                 mbar_arrive_expect_tx(bar_q, TILE);
-                tma_load_4d(s_base + OFF_Q, &tm_q, 0, qt * QM, h, z, bar_q);
-                tma_load_4d(s_base + OFF_Q + HALF, &tm_q, 64, qt * QM, h, z, bar_q);
+#pragma unroll
+                for (int hf = 0; hf < DH; ++hf)
+                    tma_load_4d(s_base + OFF_Q + hf * HALF, &tm_q, hf * 64, qt * QM, h, z, bar_q);
             }
             const int page0 = my_page(0), page1 = nt > 1 ? my_page(1) : 0;
             load_k(0, page0);
@@ -231,7 +244,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     if (warp >= 8) {
         // ====== two issuing warps: 8 loads K and issues S = Q K^T, 9 loads V and issues O += P V ======
         // Lane 0 waits and issues the products; the whole warp takes part in the loads.
-        const uint32_t idesc_s = instr_desc(BF16, false), idesc_pv = instr_desc(BF16, true);
+        const uint32_t idesc_s = instr_desc(BF16, false, KN), idesc_pv = instr_desc(BF16, true, D);
         bool alive = true;
         if (warp == 8 && nt > 0 && (PAGED || lane == 0)) {     // contiguous: lane 0 alone
             // descriptors of the tiles' first 16-wide step; a step further on adds its byte offset / 16
@@ -276,7 +289,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
                     alive = mbar_wait(bar_v + st * 8, (t >> 1) & 1, a.status, qt) && alive;
                     if (alive) {
                         umma::fence_after_sync();
-                        const uint64_t dps = dp + uint64_t(st * (TILE >> 4)), dvs = dv + uint64_t(st * (TILE >> 4));
+                        const uint64_t dps = dp + uint64_t(st * (TILE_P >> 4)), dvs = dv + uint64_t(st * (TILE >> 4));
 #pragma unroll
                         for (int ks = 0; ks < KN / 16; ++ks) {    // 16 prefix rows per step
                             const uint64_t aoff = ((ks >> 2) * HALF + (ks & 3) * 32) >> 4;
@@ -304,7 +317,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         const int r = tid & 127, g = tid >> 7;            // my query row (TMEM lane r) and group
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem_s0 + g * 128, tmem_og = tmem_o + g * 128;
-        unsigned char *prow = smem + OFF_P + g * TILE + r * 128;   // my row of P buffer g
+        unsigned char *prow = smem + OFF_P + g * TILE_P + r * 128; // my row of P buffer g
         const float c2 = a.scale_log2;
         float m_ref = -INFINITY, l = 0.f;                 // reference point of the exponent, row sum
         bool alive = true;
@@ -454,6 +467,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         for (int i = 0; i < RPW; ++i) {
             const int rr = warp * RPW + i, grow = qt * QM + rr;
             const float g0 = __shfl_sync(0xffffffffu, f0, i), g1 = __shfl_sync(0xffffffffu, f1, i);
+            if (lane >= D / 4) continue;                  // a row is D / 4 chunks of four floats
             const int sw = (lane ^ (rr & 7)) << 2;
             const float4 v0 = *reinterpret_cast<const float4 *>(stage + rr * D + sw);
             const float4 v1 = *reinterpret_cast<const float4 *>(stage + (128 + rr) * D + sw);
@@ -472,11 +486,11 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
 }
 
 // rank-4 map with 64-column x 128-row boxes
-static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int rows, int H, int Z,
+static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int D, int rows, int H, int Z,
                              int64_t stride_n, int64_t stride_h, int64_t stride_z) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {cuuint64_t(umma::D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
+    const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
     const cuuint64_t strides[3] = {cuuint64_t(stride_n) * 2, cuuint64_t(stride_h) * 2, cuuint64_t(stride_z) * 2};
     const cuuint32_t box[4] = {64, 128, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -487,12 +501,10 @@ static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int 
 }
 
 // rank-4 map over a page pool (columns, rows of a page, K/V heads, pages) with 64-column x page boxes
-static bool make_map_pool(CUtensorMap *map, const void *base, bool bf16, const PagedArgs &pg, int H_kv,
-                          const void *pool) {
-    (void)base;
+static bool make_map_pool(CUtensorMap *map, bool bf16, int D, const PagedArgs &pg, int H_kv, const void *pool) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {cuuint64_t(umma::D), cuuint64_t(pg.page_size), cuuint64_t(H_kv), cuuint64_t(pg.n_pages)};
+    const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(pg.page_size), cuuint64_t(H_kv), cuuint64_t(pg.n_pages)};
     const cuuint64_t strides[3] = {cuuint64_t(pg.stride_row) * 2, cuuint64_t(pg.stride_head) * 2,
                                    cuuint64_t(pg.stride_page) * 2};
     const cuuint32_t box[4] = {64, cuuint32_t(pg.page_size), 1, 1};
@@ -503,26 +515,26 @@ static bool make_map_pool(CUtensorMap *map, const void *base, bool bf16, const P
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, bool PAGED>
+template <typename T, int D, bool PAGED>
 static cudaError_t launch_prefix_t(const AttnArgs &a, const PagedArgs *pg, int n_runs, int first_slot,
                                    cudaStream_t stream) {
     constexpr bool bf16 = !std::is_same<T, __half>::value;
     alignas(64) CUtensorMap tq, tk, tv;
-    if (!make_map_rows128(&tq, a.q, bf16, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z)) return cudaErrorNotSupported;
+    if (!make_map_rows128(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z)) return cudaErrorNotSupported;
     if (PAGED) {
-        if (!make_map_pool(&tk, nullptr, bf16, *pg, a.H / a.kv_group, pg->k_pool) ||
-            !make_map_pool(&tv, nullptr, bf16, *pg, a.H / a.kv_group, pg->v_pool))
+        if (!make_map_pool(&tk, bf16, D, *pg, a.H / a.kv_group, pg->k_pool) ||
+            !make_map_pool(&tv, bf16, D, *pg, a.H / a.kv_group, pg->v_pool))
             return cudaErrorNotSupported;
-    } else if (!make_map_rows128(&tk, a.k, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-               !make_map_rows128(&tv, a.v, bf16, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z)) {
+    } else if (!make_map_rows128(&tk, a.k, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
+               !make_map_rows128(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z)) {
         return cudaErrorNotSupported;
     }
     static bool configured_on[kMaxDevices] = {};
     const int slot = current_device_slot();
     if (slot < 0) return cudaErrorInvalidDevice;
     if (!configured_on[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             umma::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T, D, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             umma::Geo<D>::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured_on[slot] = true;
     }
@@ -536,27 +548,34 @@ static cudaError_t launch_prefix_t(const AttnArgs &a, const PagedArgs *pg, int n
         pa.n_pages = pg->n_pages;
     }
     dim3 grid((a.n_q + umma::QM - 1) / umma::QM, a.H, a.Z * n_runs);
-    prefix_umma_kernel<T, PAGED><<<grid, PFX_THREADS, umma::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
+    prefix_umma_kernel<T, D, PAGED><<<grid, PFX_THREADS, umma::Geo<D>::SMEM_BYTES, stream>>>(a, pa, tq, tk, tv);
     return cudaGetLastError();
+}
+
+template <bool PAGED>
+static cudaError_t launch_prefix_any(const AttnArgs &a, const PagedArgs *pg, int dtype, int n_runs, int first_slot,
+                                     cudaStream_t stream) {
+    if ((a.D != 64 && a.D != 128) || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
+    if (dtype == FST_F16)
+        return a.D == 128 ? launch_prefix_t<__half, 128, PAGED>(a, pg, n_runs, first_slot, stream)
+                          : launch_prefix_t<__half, 64, PAGED>(a, pg, n_runs, first_slot, stream);
+    if (dtype == FST_BF16)
+        return a.D == 128 ? launch_prefix_t<__nv_bfloat16, 128, PAGED>(a, pg, n_runs, first_slot, stream)
+                          : launch_prefix_t<__nv_bfloat16, 64, PAGED>(a, pg, n_runs, first_slot, stream);
+    return cudaErrorNotSupported;
 }
 
 // Partial results of the prefix, split into n_runs runs, into slots first_slot .. first_slot+n_runs-1.
 cudaError_t launch_prefix_umma(const AttnArgs &a, int dtype, int n_runs, int first_slot, cudaStream_t stream) {
-    if (a.D != umma::D || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
-    if (dtype == FST_F16) return launch_prefix_t<__half, false>(a, nullptr, n_runs, first_slot, stream);
-    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16, false>(a, nullptr, n_runs, first_slot, stream);
-    return cudaErrorNotSupported;
+    return launch_prefix_any<false>(a, nullptr, dtype, n_runs, first_slot, stream);
 }
 
 // The same with the prefix rows in a page pool; a.k / a.v are not read.
 cudaError_t launch_prefix_umma_paged(const AttnArgs &a, const PagedArgs &pg, int dtype, int n_runs, int first_slot,
                                      cudaStream_t stream) {
-    if (a.D != umma::D || a.prefix <= 0 || n_runs < 1) return cudaErrorNotSupported;
     if (pg.page_size != 16 && pg.page_size != 32 && pg.page_size != 64 && pg.page_size != 128)
         return cudaErrorNotSupported;
-    if (dtype == FST_F16) return launch_prefix_t<__half, true>(a, &pg, n_runs, first_slot, stream);
-    if (dtype == FST_BF16) return launch_prefix_t<__nv_bfloat16, true>(a, &pg, n_runs, first_slot, stream);
-    return cudaErrorNotSupported;
+    return launch_prefix_any<true>(a, &pg, dtype, n_runs, first_slot, stream);
 }
 
 }  // namespace fst

@@ -48,7 +48,7 @@ _SMS = {}
 def _pick_splits(kv_splits, q, prefix, block_m, kernel):
     """(runs the shared prefix is cut into, whether a workspace is needed).
 
-    Only the tensor-core kernels split.  With head_dim 128 and at least 256 prefix rows the
+    Only the tensor-core kernels split.  With head_dim 64 or 128 and at least 256 prefix rows the
     prefix goes to the tcgen05 kernel: one CTA per 128 query rows, head, batch element and run.
     Its shared memory allows one CTA per SM, so the automatic choice is as many runs as keep the
     grid within one wave, each at least 256 rows.  Otherwise the tree kernel walks the prefix
@@ -61,7 +61,7 @@ def _pick_splits(kv_splits, q, prefix, block_m, kernel):
     if sms is None:
         sms = _SMS[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
     z_cap = 65535 // max(q.shape[0], 1)
-    if q.shape[-1] == 128 and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
+    if q.shape[-1] in (64, 128) and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
         if kv_splits is not None:
             return max(1, min(int(kv_splits), z_cap)), True
         ctas = q.shape[0] * q.shape[1] * -(-q.shape[2] // 128)
@@ -83,7 +83,7 @@ def launch_plan(q, prefix, block_m, kernel: str = "auto", kv_splits: Optional[in
         and block_m in (16, 32, 64, 128)
     tree = "attn_simt_kernel" if kernel == "simt" or not tensor_core else \
         "attn_mma_kernel" if kernel == "mma" or block_m == 16 else "attn_tma_kernel"
-    if need_ws and q.shape[-1] == 128 and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
+    if need_ws and q.shape[-1] in (64, 128) and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
         return {"kernels": ["prefix_umma_kernel", tree, "combine_splits_kernel"], "prefix_runs": splits}
     if need_ws:
         return {"kernels": [tree, "combine_splits_kernel"], "prefix_runs": splits}
@@ -194,7 +194,7 @@ def fst_attention_paged(q, k_tree, v_tree, meta: TreeMetadata, k_pool, v_pool, b
                         sm_scale, *, max_prefix: Optional[int] = None, pool_layout: str = "NHD",
                         kv_splits: Optional[int] = None, out: Optional[torch.Tensor] = None,
                         return_lse: bool = False):
-    """Tree attention behind a prefix held in a paged KV cache (head_dim 128, fp16 / bf16).
+    """Tree attention behind a prefix held in a paged KV cache (head_dim 64 or 128, fp16 / bf16).
 
     ``q`` is ``[Z, H, N, D]``; ``k_tree``, ``v_tree`` are the tree nodes' own K/V rows,
     ``[Z, H_kv, N, D]``.  The prefix of batch element ``z`` is rows ``[0, prefix_lens[z])`` of

@@ -53,7 +53,7 @@ enum fst_kernel {
     FST_KERNEL_TMA_T32 = 4,        /* ... forced 32-column tiles (three CTAs per SM)             */
     FST_KERNEL_TMA_T64 = 5,        /* ... forced 64-column tiles (fewest softmax rounds)         */
     FST_KERNEL_TMA_UMMA = 6        /* tree part as FST_KERNEL_TMA, shared prefix by the tcgen05  */
-                                   /* kernel (head_dim 128, fst_attention_fwd_splitkv only)      */
+                                   /* kernel (head_dim 64 / 128, fst_attention_fwd_splitkv only) */
 };
 
 int fst_version(void);
@@ -157,7 +157,7 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * to fill the GPU (the reference walks the prefix in one program, fstattention.py:113-136).
  * Partial results (fp32) and their log-sum-exps pass through `workspace`
  * (fst_attention_split_workspace_bytes bytes, 16-byte aligned, scratch) and a second kernel merges
- * them.  With head_dim 128 and at least 256 prefix rows FST_KERNEL_AUTO hands the prefix to a
+ * them.  With head_dim 64 or 128 and at least 256 prefix rows FST_KERNEL_AUTO hands the prefix to a
  * tcgen05/TMEM kernel (128 x 128 tiles, dense) in kv_splits runs and keeps the tree part in the
  * tree kernel; FST_KERNEL_TMA_UMMA forces that, FST_KERNEL_TMA* forces the tree kernel to walk
  * the prefix itself in kv_splits runs.  Without a prefix this is fst_attention_fwd.
@@ -203,7 +203,7 @@ int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, 
  * row r sits in page block_table[z * table_stride + r / page_size] at row r % page_size.
  * k_pool / v_pool: element (page, row, head, d) at page * pool_stride_page + row * pool_stride_row
  * + head * pool_stride_head + d (element strides, multiples of 8).  page_size 16, 32, 64 or 128;
- * head_dim 128; fp16 / bf16.  max_prefix >= every prefix_lens[z] (it sizes the grid; lengths
+ * head_dim 64 or 128; fp16 / bf16.  max_prefix >= every prefix_lens[z] (it sizes the grid; lengths
  * above it are cut).  The prefix goes to the tcgen05 kernel in kv_splits runs, the tree part to
  * the tree kernel, partial results through `workspace`
  * (fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits) bytes).  A page number

@@ -297,8 +297,8 @@ def test_prefix_split_over_ctas(fst, prefix, splits):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_prefix_with_head_dim_64(fst, dtype):
-    """head_dim 64 has no tcgen05 prefix kernel: the tree kernel walks the prefix, alone or split
-    over CTAs, and the automatic choice must pick that without being asked."""
+    """head_dim 64: the tcgen05 prefix kernel (64-column Q / K / V tiles), the tree kernel walking
+    the prefix alone or split over CTAs, and the automatic choice."""
     from fstattention_b200 import configs
     par = configs.left_weighted_tree()
     n, H, D, prefix = 256, 3, 64, 900
@@ -307,11 +307,10 @@ def test_prefix_with_head_dim_64(fst, dtype):
     exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
     meta = fst.build_tree_metadata(par, 64, 64)
     tol = TOL_F16 if dtype == torch.float16 else TOL_BF16
-    for kern, splits in (("auto", None), ("auto", 4), ("tma_t32", 3), ("tma_t64", 1), ("mma", None), ("simt", None)):
+    for kern, splits in (("auto", None), ("auto", 4), ("tma_umma", 1), ("tma_umma", 3), ("tma_t32", 3),
+                         ("tma_t64", 1), ("mma", None), ("simt", None)):
         out = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern, kv_splits=splits)
         assert maxabs(out.cpu(), exact) <= tol, (kern, splits, maxabs(out.cpu(), exact))
-    with pytest.raises(RuntimeError):
-        fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel="tma_umma", kv_splits=2)
     assert fst.last_status() == 0
 
 
@@ -425,15 +424,16 @@ def _scatter_into_pages(k, v, prefix_lens, page_size, layout, seed):
     return k_pool, v_pool, table
 
 
-@pytest.mark.parametrize("page_size,layout,dtype", [(16, "NHD", torch.float16), (64, "HND", torch.float16),
-                                                   (128, "NHD", torch.bfloat16), (32, "NHD", torch.float16)])
-def test_paged_prefix(fst, page_size, layout, dtype):
+@pytest.mark.parametrize("page_size,layout,dtype,D", [(16, "NHD", torch.float16, 128), (64, "HND", torch.float16, 128),
+                                                     (128, "NHD", torch.bfloat16, 128), (32, "NHD", torch.float16, 128),
+                                                     (16, "HND", torch.float16, 64)])
+def test_paged_prefix(fst, page_size, layout, dtype, D):
     """Prefix rows in a shuffled page pool with a different length per batch element, tree rows
     in their own tensors, grouped K/V heads: equal to attention over the same rows laid out
     contiguously (oracle), and to the contiguous tcgen05 path where the lengths allow."""
     from fstattention_b200 import configs
     par = configs.left_weighted_tree()
-    n, H, H_kv, D = 256, 4, 2, 128
+    n, H, H_kv = 256, 4, 2
     prefix_lens = [700, 129, 1024]
     Z, p_max = len(prefix_lens), max(prefix_lens)
     q, _, _ = make_qkv(Z, H, n, n, D, dtype, seed=71)
