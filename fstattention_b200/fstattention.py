@@ -102,11 +102,10 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     Alternatively pass a ``TreeMetadata`` as ``ancestor_idx`` and leave the other two ``None``;
     its block size and ancestor bound are used.  Metadata with a leading tree dimension of size
     ``Z`` gives every batch element its own tree.  ``k`` and ``v`` may have fewer heads than ``q``
-    (grouped-query attention, ``H`` a multiple of ``H_kv``; packed metadata only).
+    (grouped-query attention, ``H`` a multiple of ``H_kv``).
 
     ``kv_splits`` cuts a shared prefix into that many runs handled by separate CTAs and merged
-    afterwards (packed metadata only); ``None`` picks a split that fills the GPU when the tree
-    alone does not.
+    afterwards; ``None`` picks a split that fills the GPU when the tree alone does not.
 
     Asserts like the reference (fstattention.py:155-157): equal head dims, in {16, 32, 64, 128}.
     """
@@ -147,25 +146,11 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 raise ValueError("BLOCK_M / MAX_ANCESTORS differ from the ones the metadata was built with")
             if meta.n_blocks != -(-n_q // BLOCK_M):
                 raise ValueError("metadata block count does not match q")
-            splits, need_ws = _pick_splits(kv_splits, q, n_kv - n_q, BLOCK_M, kernel)
-            ws, ws_bytes = None, 0
-            if need_ws:
-                ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, splits))
-                ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-            tail = (BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern, splits,
-                    ws.data_ptr() if ws is not None else None, ws_bytes, status.data_ptr(), stream)
-            head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                    lse.data_ptr() if lse is not None else None,
-                    meta.packed.data_ptr(), meta.tree_stride if meta.n_trees > 1 else 0)
-            if H_kv == H:
-                rc = lib.fst_attention_fwd_splitkv(*head, *common_shape, *tail)
-            else:                                         # grouped-query attention
-                rc = lib.fst_attention_fwd_gqa(*head, Z, H, H_kv, *common_shape[2:], *tail)
-            _lib.check(rc, "fst_attention_fwd")
+            packed_ptr, packed_stride = meta.packed.data_ptr(), (meta.tree_stride if meta.n_trees > 1 else 0)
         else:
+            # the reference's three tensors (fstattention.py:153): packed here, one more launch,
+            # with the prefix length as index base (its test shifts the indices, sentinels included)
             ai, am, li = ancestor_idx, ancestor_mask, leaf_idx
-            if H_kv != H:
-                raise ValueError("grouped-query attention needs packed metadata (build_tree_metadata)")
             if am is None or li is None:
                 raise TypeError("ancestor_mask and leaf_idx are required with plain tensors")
             if not (ai.is_cuda and am.is_cuda and li.is_cuda):
@@ -177,16 +162,30 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 raise ValueError("metadata shapes do not match BLOCK_M / MAX_ANCESTORS / q")
             if ai.dtype != torch.long or li.dtype != torch.long or am.dtype not in (torch.bool, torch.uint8):
                 raise TypeError("metadata dtypes must be int64 / bool / int64")
+            if n_meta not in (1, Z):
+                raise ValueError("metadata must describe one tree or one tree per batch element")
             ai, am, li = ai.contiguous(), am.contiguous(), li.contiguous()
-            ws_bytes = int(lib.fst_attention_ref_workspace_bytes(n_meta, n_q, BLOCK_M, MAX_ANCESTORS))
+            stride = int(lib.fst_packed_meta_bytes(nb, BLOCK_M, MAX_ANCESTORS))
+            packed = torch.empty((n_meta, stride), dtype=torch.uint8, device=dev)
+            rc = lib.fst_pack_metadata(ai.data_ptr(), am.data_ptr(), li.data_ptr(), n_meta, nb, BLOCK_M,
+                                       MAX_ANCESTORS, n_kv - n_q, packed.data_ptr(), stride,
+                                       status.data_ptr(), stream)
+            _lib.check(rc, "fst_pack_metadata")
+            packed_ptr, packed_stride = packed.data_ptr(), (stride if n_meta > 1 else 0)
+        splits, need_ws = _pick_splits(kv_splits, q, n_kv - n_q, BLOCK_M, kernel)
+        ws, ws_bytes = None, 0
+        if need_ws:
+            ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, splits))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-            rc = lib.fst_attention_fwd_ref(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                lse.data_ptr() if lse is not None else None,
-                ai.data_ptr(), am.data_ptr(), li.data_ptr(), n_meta,
-                *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern,
-                ws.data_ptr(), ws_bytes, status.data_ptr(), stream)
-            _lib.check(rc, "fst_attention_fwd_ref")
+        tail = (BLOCK_M, MAX_ANCESTORS, float(sm_scale), _DTYPES[q.dtype], kern, splits,
+                ws.data_ptr() if ws is not None else None, ws_bytes, status.data_ptr(), stream)
+        head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                lse.data_ptr() if lse is not None else None, packed_ptr, packed_stride)
+        if H_kv == H:
+            rc = lib.fst_attention_fwd_splitkv(*head, *common_shape, *tail)
+        else:                                             # grouped-query attention
+            rc = lib.fst_attention_fwd_gqa(*head, Z, H, H_kv, *common_shape[2:], *tail)
+        _lib.check(rc, "fst_attention_fwd")
     return (o, lse) if return_lse else o
 
 
