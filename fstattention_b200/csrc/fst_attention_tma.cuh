@@ -292,10 +292,26 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         }
     };
     uint32_t w0n[TP], w1n[TP];                            // words of the next gathered tile
-    if (nblk == 0) gathered_words(0, w0n, w1n);
+    // With several block tiles, those in which none of my warp's 16 rows has a column are passed
+    // over outright (a block tile needs no CTA-wide step, so the warps need not agree); with
+    // rows numbered breadth first that is every block tile but the one on the diagonal.  With a
+    // single block tile there is nothing to pass over and the bookkeeping would only cost time.
+    constexpr bool SKIP = SM::NBT > 1;
+    uint32_t blk_live = 0xffffffffu;
+    if (SKIP) {
+        gathered_words(0, w0n, w1n);
+        blk_live = 0u;
+#pragma unroll
+        for (int q = 0; q < BW; ++q)
+            if (__reduce_or_sync(0xffffffffu, wb0[q] | wb1[q]) != 0u) blk_live |= 1u << (q / TP);
+    } else if (nblk == 0) {
+        gathered_words(0, w0n, w1n);
+    }
+    bool v_here = false;                                  // the block's V rows have been waited for
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < nblk;
+        if (SKIP && blk && !((blk_live >> i) & 1u)) continue;
         const int e = i - nblk;                           // gathered tile number
         uint32_t w0[TP], w1[TP];                          // mask words of my two rows for this column tile
 #pragma unroll
@@ -311,7 +327,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 w1[p] = w1n[p];
             }
         }
-        if (e + 1 >= 0) gathered_words(e + 1, w0n, w1n);  // from the last block tile on
+        if (SKIP ? !blk : e + 1 >= 0) gathered_words(e + 1, w0n, w1n);   // (single block tile: from that tile on)
         uint32_t kbase, vbase;
         if (blk) {
             kbase = s_base + SM::KB + i * TP * SM::TILE;
@@ -415,7 +431,10 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             }
         }
 
-        if (blk && i == 0) alive = mbar_wait(bar_v, 0, a.status, b) && alive;   // the block's V rows
+        if (blk && (SKIP ? !v_here : i == 0)) {           // the block's V rows, before their first use
+            alive = mbar_wait(bar_v, 0, a.status, b) && alive;
+            v_here = true;
+        }
 
         if (any) {
             // ---- O += P V
