@@ -465,6 +465,32 @@ def test_paged_prefix(fst, page_size, layout, dtype, D):
     assert fst.last_status() == 0
 
 
+def test_paged_prefix_with_an_empty_sequence(fst):
+    """One batch element has no prefix at all (and junk in its block-table row): it gets plain
+    tree attention while its neighbours get theirs behind their prefixes."""
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D, page_size = 256, 2, 128, 32
+    prefix_lens = [300, 0, 65]
+    Z, p_max = len(prefix_lens), max(prefix_lens)
+    q, _, _ = make_qkv(Z, H, n, n, D, torch.float16, seed=91)
+    _, k, v = make_qkv(Z, H, n, p_max + n, D, torch.float16, seed=92)
+    scale = D ** -0.5
+    meta = fst.build_tree_metadata(par, 64, 64)
+    k_pool, v_pool, table = _scatter_into_pages(k, v, prefix_lens, page_size, "NHD", seed=93)
+    k_tree, v_tree = k[:, :, p_max:].contiguous(), v[:, :, p_max:].contiguous()
+    lens = torch.tensor(prefix_lens, dtype=torch.int32)
+    out, lse = fst.fst_attention_paged(q.cuda(), k_tree.cuda(), v_tree.cuda(), meta, k_pool.cuda(), v_pool.cuda(),
+                                       table.cuda(), lens.cuda(), scale, kv_splits=2, return_lse=True)
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    for z, pz in enumerate(prefix_lens):
+        kz = torch.cat([k[z:z + 1, :, :pz], k[z:z + 1, :, p_max:]], dim=2)
+        vz = torch.cat([v[z:z + 1, :, :pz], v[z:z + 1, :, p_max:]], dim=2)
+        exact = oracle_attention(q[z:z + 1], kz, vz, par, scale, prefix=pz, compute_dtype=torch.float32)
+        assert maxabs(out[z:z + 1].cpu(), exact) <= TOL_F16, (z, maxabs(out[z:z + 1].cpu(), exact))
+    assert fst.last_status() == 0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
