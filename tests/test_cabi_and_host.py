@@ -22,6 +22,29 @@ def test_library_exports_every_declared_symbol(built_lib):
     assert set(_lib.EXPORTS) == declared
 
 
+def test_bindings_match_the_header(built_lib):
+    """Every ctypes prototype has as many arguments, of the right kind, as the header declares."""
+    import ctypes as C
+    header = open(os.path.join(ROOT, "include", "fstattn_b200.h")).read()
+    code = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    from fstattention_b200 import _lib
+    lib = _lib.lib()
+    kinds = {"int": C.c_int, "int64_t": C.c_int64, "size_t": C.c_size_t, "float": C.c_float}
+    for name, params in re.findall(r"\b(fst_[a-z_0-9]+)\s*\(([^)]*)\)\s*;", code):
+        params = params.strip()
+        want = []
+        if params != "void":
+            for prm in params.split(","):
+                prm = " ".join(prm.split())
+                if "*" in prm:
+                    want.append(C.c_void_p)
+                else:
+                    want.append(kinds[prm.rsplit(" ", 1)[0].replace("const ", "")])
+        got = list(getattr(lib, name).argtypes)
+        got = [C.c_void_p if t in (C.c_char_p,) else t for t in got]
+        assert got == want, (name, len(got), len(want))
+
+
 def test_host_only_entry_points(built_lib):
     from fstattention_b200 import _lib
     lib = _lib.lib()
