@@ -529,6 +529,9 @@ template <typename T, int D>
 __global__ void __launch_bounds__(128)
 combine_splits_kernel(const AttnArgs a) {
     constexpr int CPR = D / 4;                            // threads per row
+    // launched with programmatic stream serialisation: resident while the kernels that write the
+    // partial results drain, running once they have finished
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const size_t rows = size_t(a.Z) * a.H * a.n_q;
     const size_t idx = size_t(blockIdx.x) * 128 + threadIdx.x;
     const size_t row = idx / CPR;
@@ -580,8 +583,16 @@ combine_splits_kernel(const AttnArgs a) {
 template <typename T, int D>
 cudaError_t launch_combine_t(const AttnArgs &a, cudaStream_t stream) {
     const size_t items = size_t(a.Z) * a.H * a.n_q * (D / 4);
-    combine_splits_kernel<T, D><<<unsigned((items + 127) / 128), 128, 0, stream>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned((items + 127) / 128));
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, combine_splits_kernel<T, D>, a);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -144,6 +144,7 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
     constexpr int TILE = G::TILE, OFF_Q = G::OFF_Q, OFF_P = G::OFF_P, OFF_K = G::OFF_K, OFF_V = G::OFF_V,
                   OFF_BAR = G::OFF_BAR;
 
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");   // the merge kernel may take its place
     extern __shared__ unsigned char smem_raw[];
     const uint32_t s_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem = smem_raw + (s_base - smem_u32(smem_raw));
