@@ -383,7 +383,17 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
             // is tracked (one pass over S).  Only if a row of my warp has outgrown its reference
             // by more than 2^8 (always on the first tile) is the reference moved, O_g rescaled,
             // and the tile done again.
-            if (n_mine == 0) sweep(no, yes, cols);        // maximum only
+            if (n_mine == 0) {
+                // first tile: the maximum of the first 32 columns is reference enough to start
+                // with (should a later column outgrow it by 2^8 the tile is redone below)
+                uint32_t f[32];
+                tmem_ld32(f, tmem_s + lane_base);
+                tmem_ld_wait(f);
+                mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (i < cols) mx = fmaxf(mx, __uint_as_float(f[i]));
+            }
 #pragma unroll 1
             for (int pass = 0; pass < 2; ++pass) {
                 if (pass == 1 || n_mine == 0) {
