@@ -491,6 +491,44 @@ def test_paged_prefix_with_an_empty_sequence(fst):
     assert fst.last_status() == 0
 
 
+def test_prefix_path_from_two_threads_on_their_own_streams(fst):
+    """The forked prefix path keeps its helper stream per host thread: two threads, each on its
+    own stream, calling it at the same time get what a single call gets."""
+    import threading
+    from fstattention_b200 import configs
+    par = configs.left_weighted_tree()
+    n, H, D, prefix = 256, 4, 128, 1024
+    meta = fst.build_tree_metadata(par, 64, 64)
+    scale = D ** -0.5
+    data = [tuple(t.cuda() for t in make_qkv(1, H, n, prefix + n, D, torch.float16, seed=100 + i)) for i in range(2)]
+    want = [fst.fst_attention(q, k, v, meta, sm_scale=scale, kernel="tma_umma", kv_splits=2) for q, k, v in data]
+    torch.cuda.synchronize()
+    got = [None, None]
+    errors = []
+
+    def worker(i):
+        try:
+            stream = torch.cuda.Stream()
+            q, k, v = data[i]
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    out = fst.fst_attention(q, k, v, meta, sm_scale=scale, kernel="tma_umma", kv_splits=2)
+            stream.synchronize()
+            got[i] = out
+        except Exception as exc:                          # surfaced in the main thread below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    for i in range(2):
+        assert torch.equal(got[i], want[i]), i
+    assert fst.last_status() == 0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
