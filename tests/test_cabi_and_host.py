@@ -182,3 +182,20 @@ def test_dfs_order_is_a_valid_renumbering_and_shrinks_the_gather():
         assert all(last[i] == i + size[i] - 1 for i in range(n))
     order, dfs_parent = fst.dfs_order(bfs_parent)
     assert _gathered_rows(dfs_parent, 64) * 5 < _gathered_rows(bfs_parent, 64)
+
+
+@pytest.mark.gpu
+def test_c_program_against_the_library(built_lib, tmp_path):
+    """tests/cabi/cabi_example.cu - a caller with no Python and no torch - builds against the header
+    and the shared library, runs precompute + attention and agrees with its own host loop."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = str(tmp_path / "cabi_example")
+    libdir = os.path.dirname(built_lib)
+    subprocess.run([nvcc, "-O2", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cabi", "cabi_example.cu"),
+                    "-L", libdir, "-lfstattn_b200", "-Xlinker", "-rpath", "-Xlinker", libdir, "-o", exe],
+                   check=True, capture_output=True, timeout=300)
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "max-abs difference" in run.stdout
