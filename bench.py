@@ -158,7 +158,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._halt.wait(0.05)
+            self._halt.wait(0.002)                        # the timed region is a few milliseconds
 
     def stop(self):
         self._halt.set()
