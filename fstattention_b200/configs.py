@@ -120,7 +120,7 @@ def workload(name: str, step: int = 0) -> Workload:
                         block_m=64, max_ancestors=64)
     if name == "random1024":
         return Workload(name, [random_window_tree(step)], heads=32, head_dim=128, dtype="fp16",
-                        block_m=64, max_ancestors=256,
+                        block_m=64, max_ancestors=320,      # seeds 0..99 need up to 257 per block
                         notes="tree regenerated every step; step index is the seed")
     if name == "forest64":
         return Workload(name, jittered_forest(0, 64, 256), heads=32, head_dim=128, dtype="fp16",
