@@ -22,7 +22,7 @@ EXPORTS = ("fst_version", "fst_status_string", "fst_packed_meta_bytes", "fst_pre
            "fst_pack_metadata", "fst_attention_fwd", "fst_attention_ref_workspace_bytes",
            "fst_attention_fwd_ref", "fst_attention_fwd_ref_static",
            "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv", "fst_attention_fwd_gqa", "fst_dfs_order",
-           "fst_attention_fwd_paged")
+           "fst_attention_fwd_paged", "fst_selftest_wait_timeout")
 STATIC_SCRATCH_BYTES = 512 * 1024
 
 _lib = None
@@ -50,6 +50,8 @@ def _declare(lib):
     lib.fst_attention_fwd_splitkv.restype = _i
     lib.fst_attention_fwd_splitkv.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i]
                                               + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _i, _p, _sz, _p, _p])
+    lib.fst_selftest_wait_timeout.restype = _i
+    lib.fst_selftest_wait_timeout.argtypes = [_p, _p, _p]
     lib.fst_dfs_order.restype = _i
     lib.fst_dfs_order.argtypes = [_p, _i, _i, _p, _p, _p, _p]
     lib.fst_attention_fwd_paged.restype = _i

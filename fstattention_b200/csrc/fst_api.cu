@@ -148,6 +148,11 @@ int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m,
                                          static_cast<cudaStream_t>(stream)));
 }
 
+int fst_selftest_wait_timeout(int32_t *status, int32_t *done, void *stream) {
+    if (!status || !done) return FST_ERR_INVALID_ARG;
+    return cuda_status(launch_wait_timeout(status, done, static_cast<cudaStream_t>(stream)));
+}
+
 int fst_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
                   int32_t *new_parent, int32_t *status, void *stream) {
     if (!parent || !order || !new_parent || n_trees <= 0 || n_nodes <= 0) return FST_ERR_INVALID_ARG;

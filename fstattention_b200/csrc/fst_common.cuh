@@ -60,6 +60,8 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
                               void *packed, size_t packed_stride, int32_t *status,
                               cudaStream_t stream);
 
+cudaError_t launch_wait_timeout(int32_t *status, int32_t *done, cudaStream_t stream);
+
 cudaError_t launch_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
                              int32_t *new_parent, int32_t *status, cudaStream_t stream);
 

@@ -100,6 +100,16 @@ int fst_precompute(const int32_t *parent, int n_trees, int n_nodes, int block_m,
                    int32_t *status, void *stream);
 
 /*
+ * Self-test of the bounded waits (no counterpart in the reference).  Every wait on an
+ * asynchronous copy or tensor-core product in these kernels gives up after about 50 ms, records
+ * FST_DEV_TIMEOUT and lets the kernel run to its end, so that a lost completion cannot hang the
+ * GPU.  This launches one thread that waits on a barrier nobody arrives at: afterwards
+ * status[0] == FST_DEV_TIMEOUT, status[1] == 12345 and *done == 2 (1 would mean the wait
+ * returned as if somebody had arrived).  Takes about 50 ms of one SM.  Device pointers.
+ */
+int fst_selftest_wait_timeout(int32_t *status, int32_t *done, void *stream);
+
+/*
  * Depth-first renumbering of n_trees trees of n_nodes nodes each (parent as for fst_precompute),
  * the node ordering the reference leaves open (README.md:19-20; utils.py:104-129 takes the
  * caller's numbering).  order[t][i] = old index of the node that becomes node i of tree t

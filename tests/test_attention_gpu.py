@@ -529,6 +529,27 @@ def test_prefix_path_from_two_threads_on_their_own_streams(fst):
     assert fst.last_status() == 0
 
 
+def test_a_wait_that_nobody_answers_runs_out(fst):
+    """The time limit on mbarrier waits: a kernel waiting on a barrier nobody arrives at gives
+    up, reports FST_DEV_TIMEOUT and ends; the context is fine afterwards."""
+    import time
+    from fstattention_b200 import _lib
+    lib = _lib.lib()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rc = lib.fst_selftest_wait_timeout(status.data_ptr(), done.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    took = time.perf_counter() - t0
+    assert status[:2].tolist() == [19, 12345] and done.item() == 2
+    assert 0.03 <= took <= 2.0, took
+    assert "wait" in _lib.status_string(19)
+    x = torch.ones(1024, device="cuda")                      # the device still answers
+    assert x.sum().item() == 1024.0
+
+
 def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     """Attention on the depth-first renumbered tree, rows permuted in and scattered back, equals
     attention on the original numbering (and the oracle), while gathering fewer rows."""
