@@ -37,9 +37,35 @@ def last_status(device=None) -> int:
 
 
 def _strides(t):
-    if t.stride(3) != 1:
+    st = t.stride()
+    if st[3] != 1:
         raise ValueError("the head dimension must be contiguous")
-    return [t.stride(0), t.stride(1), t.stride(2)]
+    return [st[0], st[1], st[2]]
+
+
+def _raw_stream(dev) -> int:
+    """Handle of torch's current stream on ``dev`` (the private fast path when torch has it:
+    this sits on the per-layer call path of an eager decoder)."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(dev.index)
+    except AttributeError:
+        return torch.cuda.current_stream(dev).cuda_stream
+
+
+class _OnDevice:
+    """``torch.cuda.device(dev)`` that does nothing when ``dev`` is already current."""
+
+    def __init__(self, dev):
+        self.ctx = None if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
 
 
 _SMS = {}
@@ -130,13 +156,13 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     lib = _lib.lib()
     dev = q.device
     status = _status_record(dev)
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     kern = _lib.KERNELS[kernel]
     common_shape = [Z, H, n_q, n_kv, D] + _strides(q) + _strides(k) + _strides(v) + _strides(o)
 
     meta = ancestor_idx if isinstance(ancestor_idx, TreeMetadata) else \
         metadata_of(ancestor_idx, ancestor_mask, leaf_idx)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         if meta is not None:
             if meta.n_trees not in (1, Z):
                 raise ValueError("metadata must describe one tree or one tree per batch element")
@@ -242,7 +268,7 @@ def fst_attention_paged(q, k_tree, v_tree, meta: TreeMetadata, k_pool, v_pool, b
         ctas = Z * H * -(-n_q // 128)
         kv_splits = int(max(1, min(sms // max(ctas, 1), max_prefix // 256, 65535 // Z)))
     status = _status_record(dev)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         ws_bytes = int(lib.fst_attention_split_workspace_bytes(Z, H, n_q, D, kv_splits))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         rc = lib.fst_attention_fwd_paged(
@@ -254,7 +280,7 @@ def fst_attention_paged(q, k_tree, v_tree, meta: TreeMetadata, k_pool, v_pool, b
             k_pool.stride(0), k_pool.stride(row_dim), k_pool.stride(head_dim_),
             Z, H, H_kv, n_q, D, *_strides(q), *_strides(k_tree), *_strides(v_tree), *_strides(o),
             meta.block_m, meta.max_ancestors, float(sm_scale), _DTYPES[q.dtype], kv_splits,
-            ws.data_ptr(), ws_bytes, status.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            ws.data_ptr(), ws_bytes, status.data_ptr(), _raw_stream(dev))
     _lib.check(rc, "fst_attention_fwd_paged")
     return (o, lse) if return_lse else o
 
