@@ -41,7 +41,9 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per attention launch, from the ncu captures summarised
 # in profiles/attn_tma_kernel_medusa256_forest64.md (same per-launch work as the bench)
-NCU_TRAFFIC_BYTES = {"medusa256": 6.36e6, "forest64": 515.7e6}
+NCU_TRAFFIC_BYTES = {"medusa256": 6.36e6, "forest64": 515.7e6, "random1024": 25.3e6, "deep4096": 242.4e6}
+# the same for prefix_umma_kernel (profiles/prefix_umma_kernel_medusa256_prefix4096.md)
+NCU_PREFIX_TRAFFIC_BYTES = {"medusa256_prefix4096": 70.9e6}
 
 METRIC = "tree_attn_gathered_kv_bandwidth"
 UNIT = "GB/s"
@@ -433,7 +435,7 @@ def run_ours(args, rank, world):
         flops = 4.0 * D * w.block_m * (kv / (2 * D * esize))
         tf = flops / (launch_us * 1e-6) / 1e12
         roofline_tensor = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
-                           "traffic": None, "peak_source": f"of {tkind}", "kernel": "prefix_umma_kernel",
+                           "traffic": NCU_PREFIX_TRAFFIC_BYTES.get(w.name), "peak_source": f"of {tkind}", "kernel": "prefix_umma_kernel",
                            "flops_per_call": flops, "prefix_runs": plan["prefix_runs"],
                            "note": "time is the whole call: prefix kernel, tree kernel beside it, merge kernel"}
     line = {
