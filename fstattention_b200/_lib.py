@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG, "libfstattn_b200.so")
 FST_OK = 0
 STATUS_WORDS = 4
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
+KERNEL_FLAG_META_STABLE = 0x100
 KERNELS = {"auto": 0, "simt": 1, "mma": 2, "tma": 3, "tma_t32": 4, "tma_t64": 5,
            "tma_umma": 6}
 DEV_MALFORMED_TREE, DEV_ANCESTOR_OVERFLOW, DEV_INDEX_RANGE = 16, 17, 18
@@ -22,7 +23,8 @@ EXPORTS = ("fst_version", "fst_status_string", "fst_packed_meta_bytes", "fst_pre
            "fst_pack_metadata", "fst_attention_fwd", "fst_attention_ref_workspace_bytes",
            "fst_attention_fwd_ref", "fst_attention_fwd_ref_static",
            "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv", "fst_attention_fwd_gqa", "fst_dfs_order",
-           "fst_attention_fwd_paged", "fst_selftest_wait_timeout")
+           "fst_attention_fwd_paged", "fst_selftest_wait_timeout", "fst_tree_topk_nodes",
+           "fst_build_tree_topk")
 STATIC_SCRATCH_BYTES = 512 * 1024
 
 _lib = None
@@ -52,6 +54,10 @@ def _declare(lib):
                                               + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _i, _p, _sz, _p, _p])
     lib.fst_selftest_wait_timeout.restype = _i
     lib.fst_selftest_wait_timeout.argtypes = [_p, _p, _p]
+    lib.fst_tree_topk_nodes.restype = C.c_longlong
+    lib.fst_tree_topk_nodes.argtypes = [_i, _i, C.c_double]
+    lib.fst_build_tree_topk.restype = _i
+    lib.fst_build_tree_topk.argtypes = [_p, _i, _i, _i, C.c_double, _i, _p, _p, _p, _p]
     lib.fst_dfs_order.restype = _i
     lib.fst_dfs_order.argtypes = [_p, _i, _i, _p, _p, _p, _p]
     lib.fst_attention_fwd_paged.restype = _i

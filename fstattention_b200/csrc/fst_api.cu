@@ -1,4 +1,6 @@
 // C ABI of fstattn_b200: argument checks and kernel dispatch.  See include/fstattn_b200.h.
+#include <atomic>
+#include <cmath>
 #include <cstdio>
 
 #include "fst_common.cuh"
@@ -72,6 +74,7 @@ static SideStream *side_stream(cudaStream_t caller) {
 static int cuda_status(cudaError_t e) {
     if (e == cudaSuccess) return FST_OK;
     if (e == cudaErrorNotSupported) return FST_ERR_UNSUPPORTED;
+    if (e == cudaErrorInvalidConfiguration) return FST_ERR_TOO_LARGE;   // what a launcher returns when the sizes do not fit an SM
     return FST_ERR_CUDA;
 }
 }  // namespace fst
@@ -86,17 +89,16 @@ static __device__ __align__(256) unsigned char g_static_scratch[FST_STATIC_SCRAT
 // only a handle for the runtime, not something a kernel can dereference, so the address is
 // asked for once per device and remembered.
 static int static_scratch_address(void **out) {
-    constexpr int kMaxDevices = 64;
-    static void *cached[kMaxDevices] = {};
+    static std::atomic<void *> cached[kMaxDevices];       // two threads racing here store the same address
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FST_ERR_CUDA;
-    if (cached[dev] == nullptr) {
-        void *ptr = nullptr;
+    void *ptr = cached[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr)
             return FST_ERR_CUDA;
-        cached[dev] = ptr;
+        cached[dev].store(ptr, std::memory_order_release);
     }
-    *out = cached[dev];
+    *out = ptr;
     return FST_OK;
 }
 
@@ -161,6 +163,22 @@ int fst_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *orde
                                         static_cast<cudaStream_t>(stream)));
 }
 
+long long fst_tree_topk_nodes(int depth, int topk, double left_weight_factor) {
+    if (!(left_weight_factor >= 0.0) || !(left_weight_factor <= 1.0)) return -1;
+    return tree_topk_nodes(depth, topk, left_weight_factor);
+}
+
+int fst_build_tree_topk(const float *scores, int n_trees, int depth, int topk, double left_weight_factor,
+                        int max_nodes, int32_t *parent, int32_t *choice, float *node_score, void *stream) {
+    if (!scores || !parent || n_trees <= 0 || depth < 0 || topk <= 0 || max_nodes <= 0 ||
+        !(left_weight_factor >= 0.0) || !(left_weight_factor <= 1.0))
+        return FST_ERR_INVALID_ARG;
+    if (n_trees > 65535 || depth + 1 > kMaxTreeLevels || tree_topk_nodes(depth, topk, left_weight_factor) < 0)
+        return FST_ERR_TOO_LARGE;
+    return cuda_status(launch_build_tree_topk(scores, n_trees, depth, topk, left_weight_factor, max_nodes,
+                                              parent, choice, node_score, static_cast<cudaStream_t>(stream)));
+}
+
 int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
                       const int64_t *leaf_idx, int n_trees, int n_blocks, int block_m,
                       int max_ancestors, int64_t index_base, void *packed,
@@ -168,7 +186,7 @@ int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
     if (!ancestor_idx || !ancestor_mask || !leaf_idx || !packed || n_trees <= 0 || n_blocks <= 0 ||
         block_m <= 0 || max_ancestors <= 0)
         return FST_ERR_INVALID_ARG;
-    if (n_trees > 65535 || max_ancestors > 65536) return FST_ERR_TOO_LARGE;
+    if (n_trees > 65535 || max_ancestors > 32768) return FST_ERR_TOO_LARGE;   // one slot map per CTA in shared memory
     if (!aligned16(packed) || (packed_tree_stride & 15)) return FST_ERR_ALIGNMENT;
     if (n_trees > 1 && packed_tree_stride < packed_layout(n_blocks, block_m, max_ancestors).total)
         return FST_ERR_INVALID_ARG;
@@ -199,6 +217,10 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (H > 65535 || Z > 65535) return FST_ERR_TOO_LARGE;
     if (H_kv <= 0 || H % H_kv != 0) return FST_ERR_INVALID_ARG;
     if (!aligned16(packed) || (meta_tree_stride & 15)) return FST_ERR_ALIGNMENT;
+    if (!std::isfinite(sm_scale)) return FST_ERR_INVALID_ARG;   // any finite factor is fine, either sign (fstattention.py:78)
+    const int flags = kernel & ~FST_KERNEL_MASK;
+    kernel &= FST_KERNEL_MASK;
+    if (flags & ~FST_KERNEL_FLAG_META_STABLE) return FST_ERR_INVALID_ARG;
 
     AttnArgs a;
     a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse;
@@ -218,6 +240,7 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     a.part_lse = nullptr;
     a.skip_prefix = 0;
     a.part_slots = 1;
+    a.meta_stable = (flags & FST_KERNEL_FLAG_META_STABLE) ? 1 : 0;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     // the tensor-core kernel moves 16-byte pieces: every row must start on a 16-byte boundary
@@ -241,7 +264,9 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     // while the tree kernel does the tree part (head_dim 64 or 128; chosen automatically from 256
     // prefix rows on), or the tree kernel itself is launched kv_splits times over the prefix.
     const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA;
-    const bool want_umma = can_part && (head_dim == 128 || head_dim == 64) &&
+    // (the tcgen05 kernel takes Q from shared memory as it arrived, so it cannot flip Q's sign
+    // for a negative factor; the tree kernel walks the prefix itself then)
+    const bool want_umma = can_part && (head_dim == 128 || head_dim == 64) && sm_scale > 0.f &&
                            (choice == FST_KERNEL_TMA_UMMA || (automatic && a.prefix >= 256));
     if (choice == FST_KERNEL_TMA_UMMA && !want_umma) return FST_ERR_UNSUPPORTED;
     if (can_part && (want_umma || kv_splits > 1)) {
@@ -263,6 +288,8 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
             if (side != nullptr && cudaEventRecord(side->fork, st) == cudaSuccess &&
                 cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
                 tree_st = side->stream;
+            else
+                (void)cudaGetLastError();                 // no fork: same stream, and no stale error for the launches below
             e = launch_prefix_umma(a, dtype, kv_splits, 1, st);
             const cudaError_t et = launch_attention_mma(a, dtype, FST_KERNEL_TMA, tree_st);
             if (tree_st != st) {                          // always join what was forked
@@ -354,6 +381,7 @@ int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tre
         max_ancestors <= 0 || max_prefix <= 0 || n_pages <= 0 || kv_splits < 1 || table_stride <= 0)
         return FST_ERR_INVALID_ARG;
     if ((head_dim != 128 && head_dim != 64) || !mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
+    if (!(sm_scale > 0.f) || !std::isfinite(sm_scale)) return FST_ERR_INVALID_ARG;   // the tcgen05 prefix kernel wants a positive factor
     if (page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return FST_ERR_UNSUPPORTED;
     if (H > 65535 || Z > 65535 || (long long)Z * kv_splits > 65535) return FST_ERR_TOO_LARGE;
     if ((long long)table_stride * page_size < max_prefix) return FST_ERR_INVALID_ARG;
@@ -384,6 +412,7 @@ int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tre
     a.n_splits = 1;
     a.skip_prefix = 1;
     a.part_slots = kv_splits + 1;
+    a.meta_stable = 0;
     a.part_o = static_cast<float *>(workspace);
     a.part_lse = a.part_o + size_t(a.part_slots) * Z * H * n_q * head_dim;
     AttnArgs ap = a;                                      // the prefix part: rows come from the page pool
@@ -397,6 +426,8 @@ int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tre
     if (side != nullptr && cudaEventRecord(side->fork, st) == cudaSuccess &&
         cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
         tree_st = side->stream;
+    else
+        (void)cudaGetLastError();
     cudaError_t e = launch_prefix_umma_paged(ap, pg, dtype, kv_splits, 1, st);
     const cudaError_t et = launch_attention_mma(a, dtype, FST_KERNEL_TMA, tree_st);
     if (tree_st != st) {
@@ -438,7 +469,8 @@ int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, 
     return fst_attention_fwd(q, k, v, o, lse, workspace, n_meta_trees == 1 ? 0 : tree_bytes, Z, H,
                              n_q, n_kv, head_dim, q_stride_z, q_stride_h, q_stride_n, k_stride_z,
                              k_stride_h, k_stride_n, v_stride_z, v_stride_h, v_stride_n, o_stride_z,
-                             o_stride_h, o_stride_n, block_m, max_ancestors, sm_scale, dtype, kernel,
+                             o_stride_h, o_stride_n, block_m, max_ancestors, sm_scale, dtype,
+                             kernel & FST_KERNEL_MASK,    // the metadata was written a launch ago: never "stable"
                              status, stream);
 }
 

@@ -24,7 +24,8 @@
 // Arithmetic.  S = Q K^T and O += P V use mma.sync m16n8k16 with fp32 accumulation; P is rounded
 // to the input type for the second product, as in fstattention.py:102.  Q is not pre-scaled:
 // scores are scaled by sm_scale*log2(e) in fp32 inside the exponent (the reference rounds the
-// scaled Q to fp16, fstattention.py:78).  sm_scale must be positive.
+// scaled Q to fp16, fstattention.py:78).  The running maximum is tracked in raw score units, so a
+// negative sm_scale is applied as a sign flip of Q and |sm_scale| in the exponent.
 
 #pragma once
 
@@ -176,6 +177,14 @@ attn_mma_kernel(const AttnArgs a) {
             qf[ks][2] = ok0 ? __ldg(q0 + ks * 8 + 4) : 0u;
             qf[ks][3] = ok1 ? __ldg(q1 + ks * 8 + 4) : 0u;
         }
+        // a negative scale moves into Q as a sign flip (the running maximum below is kept in raw
+        // score units, which orders scores correctly only for a positive factor)
+        if (a.scale_log2 < 0.f) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) qf[ks][i] ^= 0x80008000u;
+        }
     }
 
     // ---- the block's own K and V rows: contiguous, no metadata needed
@@ -234,7 +243,7 @@ attn_mma_kernel(const AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < ND; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // m in raw score units; l is my share
-    const float c2 = a.scale_log2;
+    const float c2 = fabsf(a.scale_log2);
 
     const int n_tiles = NBLK + nt_gat;
     // mask words of my two rows for column tile i (fetched one tile ahead of their use)
@@ -399,15 +408,11 @@ template <typename T, int D, int BM>
 cudaError_t launch_mma_inst(const AttnArgs &a, cudaStream_t stream) {
     using SM = MmaSmem<D, BM>;
     constexpr size_t smem = SM::BYTES;
-    static bool configured_on[kMaxDevices] = {};           // the attribute is per device
-    const int slot = current_device_slot();
-    if (slot < 0) return cudaErrorInvalidDevice;
-    if (!configured_on[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_mma_kernel<T, D, BM>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
-        configured_on[slot] = true;
-    }
+    static DeviceOnce configured;                          // the attribute is per device
+    const cudaError_t ce = configured.run([&] {
+        return cudaFuncSetAttribute(attn_mma_kernel<T, D, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    });
+    if (ce != cudaSuccess) return ce;
     dim3 grid(a.nb, a.H, a.Z), block(BM * 2);
     attn_mma_kernel<T, D, BM><<<grid, block, smem, stream>>>(a);
     return cudaGetLastError();

@@ -21,6 +21,9 @@
 
 #include <cuda.h>
 
+#include <atomic>
+#include <memory>
+#include <new>
 #include <type_traits>
 
 #include "fst_attention_mma.cuh"
@@ -144,9 +147,14 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 
     // Launched with programmatic stream serialisation: this grid may be resident before the grid
     // ahead of it in the stream has finished.  Let the one behind us in, then wait for the one
-    // ahead (completion and memory flush) before the first global-memory access.
+    // ahead (completion and memory flush) before the first access to memory it may have written.
+    // Q, K, V and O always count as such.  The packed metadata does too, unless the caller says
+    // (a.meta_stable) that it was complete before the launch ahead of this one - the usual case:
+    // one precompute per decode step, then one attention call per layer - and then the index
+    // list, the count and the mask words are requested while the grid ahead is still draining.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    const bool early_meta = a.meta_stable != 0;
+    if (!early_meta) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     const PackedLayout L = packed_layout(a.nb, BM, a.ma);
     const int maw = L.maw;
@@ -182,14 +190,17 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         wb0[p] = (tree && ok0) ? __ldg(g_bmask + r0 * BW + p) : 0u;
         wb1[p] = (tree && ok1) ? __ldg(g_bmask + r1 * BW + p) : 0u;
     }
-
-    // ---- one thread starts the TMA transfers: Q and block K on one barrier, block V on another
-    if (tid == 0) {
+    if (tid == 0) {                                       // shared memory only: needs no wait either
         mbar_init(bar_qk, 1);
         mbar_init(bar_v, 1);
         mbar_init(bar_p, 1);
         mbar_init(bar_p + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (early_meta) asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+    // ---- one thread starts the TMA transfers: Q and block K on one barrier, block V on another
+    if (tid == 0) {
         mbar_arrive_expect_tx(bar_qk, (tree ? 2 : 1) * NB32 * SM::TILE);
 #pragma unroll
         for (int j = 0; j < NB32; ++j)
@@ -262,6 +273,15 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], qb + TL::off(qr & 31, ks * 2 + (lane >> 4)));
     }
+    // A negative scale: the running maximum below is kept in raw score units and scaled inside
+    // the exponent, which orders scores correctly only for a positive factor; so the sign moves
+    // into Q (the sign bit of both halves of every fragment register) and the factor is |scale|.
+    if (a.scale_log2 < 0.f) {
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qf[ks][i] ^= 0x80008000u;
+    }
     if (nt_gat > 1) {
         __syncthreads();
         load_gathered(1, 1, nt_ext > 1, nodeB);
@@ -273,7 +293,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
     for (int i = 0; i < ND; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // m in raw score units; l is my share
-    const float c2 = a.scale_log2;
+    const float c2 = fabsf(a.scale_log2);
 
     const int n_tiles = nblk + nt_gat;
     // mask words of my two rows for gathered tile e (external ancestors, then prefix tiles)
@@ -604,30 +624,93 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_
                                    CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn fn = cached.load(std::memory_order_acquire);
     if (fn == nullptr) {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
+            q == cudaDriverEntryPointSuccess) {
             fn = reinterpret_cast<EncodeTiledFn>(p);
+            cached.store(fn, std::memory_order_release);
+        }
     }
     return fn;
 }
 
-// rank-4 map (columns, rows, heads, batch) with 64-column x 32-row boxes, 128-byte swizzle
+// What a tensor map is made from.  Encoding one costs the driver about a microsecond, four of
+// them are needed per call and a decoder calls with the same few buffers again and again, so
+// each host thread keeps the maps it has built in a direct-mapped table keyed by these fields.
+// A map stays valid for as long as its key describes the tensor: it holds an address and a
+// shape, nothing that dies with the allocation.
+struct MapKey {
+    const void *base;
+    int64_t stride_n, stride_h, stride_z;
+    int32_t rows, H, Z, D, bf16, box_rows;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && stride_n == o.stride_n && stride_h == o.stride_h && stride_z == o.stride_z &&
+               rows == o.rows && H == o.H && Z == o.Z && D == o.D && bf16 == o.bf16 && box_rows == o.box_rows;
+    }
+};
+struct MapSlot {
+    alignas(64) CUtensorMap map;
+    MapKey key;
+    bool used = false;
+};
+constexpr int kMapSlots = 1024;
+
+inline MapSlot *map_table() {
+    thread_local std::unique_ptr<MapSlot[]> table;
+    if (!table) table.reset(new (std::nothrow) MapSlot[kMapSlots]);
+    return table.get();
+}
+
+// rank-4 map (columns, rows, heads, batch) with 64-column x box_rows boxes, 128-byte swizzle
 inline bool make_map(CUtensorMap *map, const void *base, bool bf16, int D, int rows, int H, int Z,
-                     int64_t stride_n, int64_t stride_h, int64_t stride_z) {
+                     int64_t stride_n, int64_t stride_h, int64_t stride_z, int box_rows = 32) {
+    const MapKey key{base, stride_n, stride_h, stride_z, rows, H, Z, D, bf16 ? 1 : 0, box_rows};
+    MapSlot *table = map_table();
+    MapSlot *slot = nullptr;
+    if (table != nullptr) {
+        uint64_t hsh = reinterpret_cast<uintptr_t>(base) >> 4;
+        hsh = (hsh ^ (hsh >> 17) ^ uint64_t(rows) * 0x9E3779B97F4A7C15ull ^ uint64_t(stride_n) * 0xC2B2AE3D27D4EB4Full ^
+               uint64_t(H) << 20 ^ uint64_t(Z) << 40 ^ uint64_t(box_rows) << 7) * 0xFF51AFD7ED558CCDull;
+        slot = &table[(hsh >> 40) % kMapSlots];
+        if (slot->used && slot->key == key) {
+            *map = slot->map;
+            return true;
+        }
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
     const cuuint64_t strides[3] = {cuuint64_t(stride_n) * 2, cuuint64_t(stride_h) * 2, cuuint64_t(stride_z) * 2};
-    const cuuint32_t box[4] = {64, 32, 1, 1};
+    const cuuint32_t box[4] = {64, cuuint32_t(box_rows), 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+           const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (slot != nullptr) {
+        slot->map = *map;
+        slot->key = key;
+        slot->used = true;
+    }
+    return true;
+}
+
+// number of SMs of the current device (cached)
+inline int sm_count() {
+    static std::atomic<int> cached[kMaxDevices];
+    const int slot = current_device_slot();
+    if (slot < 0) return 148;
+    int n = cached[slot].load(std::memory_order_acquire);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, slot) != cudaSuccess || n <= 0) n = 148;
+        cached[slot].store(n, std::memory_order_release);
+    }
+    return n;
 }
 
 template <typename T, int D, int BM, int TN, bool PFX>
@@ -641,15 +724,12 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
         !make_map(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
         !make_map(&to, a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z))
         return cudaErrorNotSupported;
-    static bool configured_on[kMaxDevices] = {};           // the attribute is per device
-    const int slot = current_device_slot();
-    if (slot < 0) return cudaErrorInvalidDevice;
-    if (!configured_on[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        if (e != cudaSuccess) return e;
-        configured_on[slot] = true;
-    }
+    static DeviceOnce configured;
+    const cudaError_t ce = configured.run([&] {
+        return cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    });
+    if (ce != cudaSuccess) return ce;
     if (a.n_splits < 1 || (long long)a.Z * a.n_splits > 65535) return cudaErrorInvalidValue;
     dim3 grid(a.nb, a.H, a.Z * a.n_splits), block(BM * 2);
     // Programmatic stream serialisation: the grid may become resident while the kernel ahead of
@@ -681,7 +761,7 @@ template <typename T, int D>
 cudaError_t launch_tma_d(const AttnArgs &a, int tile_cols, cudaStream_t stream) {
     if (tile_cols == 0) {
         const long long ctas = (long long)a.nb * a.H * a.Z * a.n_splits;
-        tile_cols = ctas <= 8 * 148 ? 64 : 32;
+        tile_cols = ctas <= 8LL * sm_count() ? 64 : 32;
     }
     if (tile_cols == 64) {
         switch (a.bm) {

@@ -3,6 +3,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+
+#include <atomic>
 #include <stdint.h>
 #include <stddef.h>
 
@@ -54,6 +56,22 @@ inline int current_device_slot() {
     return dev;
 }
 
+// One-time per-device launch set-up of a kernel instantiation (the dynamic shared memory
+// attribute is per device); safe from several host threads.
+struct DeviceOnce {
+    // (static storage: zero-initialised)
+    std::atomic<bool> done[kMaxDevices];
+    template <typename F>
+    cudaError_t run(F &&f) {
+        const int slot = current_device_slot();
+        if (slot < 0) return cudaErrorInvalidDevice;
+        if (done[slot].load(std::memory_order_acquire)) return cudaSuccess;
+        const cudaError_t e = f();                        // idempotent: a second thread may repeat it
+        if (e == cudaSuccess) done[slot].store(true, std::memory_order_release);
+        return e;
+    }
+};
+
 // Kernel launchers (defined in the .cu files, called from fst_api.cu)
 cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
                               int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,
@@ -64,6 +82,13 @@ cudaError_t launch_wait_timeout(int32_t *status, int32_t *done, cudaStream_t str
 
 cudaError_t launch_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *order,
                              int32_t *new_parent, int32_t *status, cudaStream_t stream);
+
+// levels (depth + 1) a device-built forest may have
+constexpr int kMaxTreeLevels = 32;
+long long tree_topk_nodes(int depth, int topk, double left_weight_factor);
+cudaError_t launch_build_tree_topk(const float *scores, int n_trees, int depth, int topk,
+                                   double left_weight_factor, int max_nodes, int32_t *parent, int32_t *choice,
+                                   float *node_score, cudaStream_t stream);
 
 cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
                         int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
@@ -90,6 +115,9 @@ struct AttnArgs {
     // own result as partial slot 0; part_slots: how many partial slots the merge kernel reads
     int skip_prefix;
     int part_slots;
+    // the packed metadata was complete before the launch ahead of this one in the stream began:
+    // a kernel launched with programmatic stream serialisation may read it before its dependency wait
+    int meta_stable;
 };
 
 // Prefix rows held in a page pool (a KV cache): pages of page_size rows, pool strides in elements.

@@ -21,6 +21,7 @@
 //
 // Also here: the converter from reference-format metadata tensors to the packed form.
 
+#include <atomic>
 #include <climits>
 
 #include "fst_common.cuh"
@@ -30,6 +31,11 @@ namespace fst {
 constexpr int PRE_THREADS = 256;
 constexpr int PRE_WARPS = PRE_THREADS / 32;
 
+// BYTE_FLAGS: ancestors are first marked as one byte per node and packed into the bitmap by
+// ballots (the fast path: plain stores never serialise).  Without it the walkers set bitmap bits
+// with atomicOr directly; that needs 1/9 of the shared memory and is what lets trees of a
+// hundred thousand nodes and more fit (a CTA keeps a bitmap of every node below its last row).
+template <bool BYTE_FLAGS>
 __global__ void __launch_bounds__(PRE_THREADS)
 precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, int ma, int par_cap, int depth_cap,
                   int64_t *__restrict__ anc_idx_all, uint8_t *__restrict__ anc_mask_all,
@@ -51,7 +57,7 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     uint32_t *blkmask = rowmask + size_t(bm) * maw;                   // [bm][bw] over block rows
     int *warp_tot = reinterpret_cast<int *>(blkmask + size_t(bm) * bw);
     unsigned char *flag = reinterpret_cast<unsigned char *>(warp_tot + 40);   // [W*32] node is an ancestor
-    int *chain = reinterpret_cast<int *>(flag + size_t(W) * 32);      // [depth_cap][bm] ancestors of row j
+    int *chain = reinterpret_cast<int *>(flag + (BYTE_FLAGS ? size_t(W) * 32 : 0));   // [depth_cap][bm] ancestors of row j
     int *depth = chain + size_t(depth_cap) * bm;                      // [bm] recorded chain length
     int *s_par = depth + bm;
 
@@ -79,7 +85,11 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
             if (i < cap) s_par[i] = checked(i, v[u]);
         }
     }
-    for (int i = tid; i < W * 8; i += PRE_THREADS) reinterpret_cast<uint32_t *>(flag)[i] = 0u;
+    if (BYTE_FLAGS) {
+        for (int i = tid; i < W * 8; i += PRE_THREADS) reinterpret_cast<uint32_t *>(flag)[i] = 0u;
+    } else {
+        for (int i = tid; i < W; i += PRE_THREADS) bitmap[i] = 0u;
+    }
     for (int i = tid; i < bm * maw; i += PRE_THREADS) rowmask[i] = 0u;
     for (int i = tid; i < bm * bw; i += PRE_THREADS) blkmask[i] = 0u;
     __syncthreads();
@@ -102,7 +112,8 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
             int a = par(k);
             while (a >= 0) {
                 if (n < depth_cap) chain[n * bm + j] = a;
-                flag[a] = 1;
+                if (BYTE_FLAGS) flag[a] = 1;
+                else atomicOr(&bitmap[a >> 5], 1u << (a & 31));
                 ++n;
                 a = par(a);
             }
@@ -112,11 +123,13 @@ precompute_kernel(const int32_t *__restrict__ parent_all, int n_nodes, int bm, i
     }
     const bool walk_masks = __syncthreads_or(too_deep) != 0;          // also: flags complete
     // flags -> bitmap, one warp per word
-    for (int w = wid; w < W; w += PRE_WARPS) {
-        const uint32_t word = __ballot_sync(0xffffffffu, flag[w * 32 + lane] != 0);
-        if (lane == 0) bitmap[w] = word;
+    if (BYTE_FLAGS) {
+        for (int w = wid; w < W; w += PRE_WARPS) {
+            const uint32_t word = __ballot_sync(0xffffffffu, flag[w * 32 + lane] != 0);
+            if (lane == 0) bitmap[w] = word;
+        }
+        __syncthreads();
     }
-    __syncthreads();
 
     // 2. exclusive popcount scan over the bitmap words -> rank[w]
     const int per = (W + PRE_THREADS - 1) / PRE_THREADS;
@@ -366,7 +379,9 @@ pack_kernel(const int64_t *__restrict__ anc_idx_all, const uint8_t *__restrict__
     }
 }
 
-static size_t g_pre_smem_set[kMaxDevices] = {};       // largest dynamic shared memory enabled, per device
+// largest dynamic shared memory enabled so far, per device and kernel variant
+static std::atomic<size_t> g_pre_smem_set[2][kMaxDevices];
+static std::atomic<size_t> g_pack_smem_set[kMaxDevices];
 
 cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, int bm, int ma,
                               int64_t *anc_idx, uint8_t *anc_mask, int64_t *leaf_idx,
@@ -375,27 +390,36 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
     const int nb = (n_nodes + bm - 1) / bm;
     const int maw = (ma + 31) / 32;
     const size_t W = (size_t(nb) * bm + 31) / 32;
+    const size_t budget = 200 * 1024;
+    // bitmap + ranks + the two row masks + scan scratch + chain lengths
+    const size_t base = (2 * W + size_t(bm) * maw + size_t(bm) * ((bm + 31) / 32) + 40 + size_t(bm)) * 4;
     // recording space for the rows' chains: as deep as 48 KB allows, at most 1024 levels
     int depth_cap = int((48 * 1024) / (size_t(bm) * 4));
     if (depth_cap > 1024) depth_cap = 1024;
     if (depth_cap < 1) depth_cap = 1;
-    const size_t fixed = (2 * W + size_t(bm) * maw + size_t(bm) * ((bm + 31) / 32) + 40 + size_t(bm)) * 4 + W * 32 +
-                         size_t(depth_cap) * bm * 4;
-    const size_t budget = 200 * 1024;
-    if (fixed + 1024 > budget) return cudaErrorInvalidValue;
+    // Byte flags (one byte per node below the last row) while they leave room to stage a good
+    // part of the parent array; beyond that the walkers set bitmap bits with atomics.
+    bool byte_flags = base + W * 32 + size_t(depth_cap) * bm * 4 + 16 * 1024 <= budget;
+    size_t fixed = base + (byte_flags ? W * 32 : 0) + size_t(depth_cap) * bm * 4;
+    while (fixed + 1024 > budget && depth_cap > 1) {     // a tight budget: record shallower chains
+        depth_cap = depth_cap / 2;                         // (deeper rows are walked a second time)
+        fixed = base + size_t(depth_cap) * bm * 4;
+    }
+    if (fixed + 1024 > budget) return cudaErrorInvalidConfiguration;
     const size_t cap = (budget - fixed) / 4;
     const int par_cap = int(cap < size_t(n_nodes) ? cap : size_t(n_nodes));
     const size_t smem = fixed + size_t(par_cap) * 4;
     const int slot = current_device_slot();
     if (slot < 0) return cudaErrorInvalidDevice;
-    if (smem > 48 * 1024 && smem > g_pre_smem_set[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(precompute_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    auto kernel = byte_flags ? precompute_kernel<true> : precompute_kernel<false>;
+    std::atomic<size_t> &enabled = g_pre_smem_set[byte_flags ? 1 : 0][slot];
+    if (smem > 48 * 1024 && smem > enabled.load(std::memory_order_acquire)) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        g_pre_smem_set[slot] = smem;
+        enabled.store(smem, std::memory_order_release);
     }
     dim3 grid(nb, n_trees);
-    precompute_kernel<<<grid, PRE_THREADS, smem, stream>>>(
+    kernel<<<grid, PRE_THREADS, smem, stream>>>(
         parent, n_nodes, bm, ma, par_cap, depth_cap, anc_idx, anc_mask, leaf_idx,
         static_cast<unsigned char *>(packed), packed_stride, status);
     return cudaGetLastError();
@@ -404,8 +428,16 @@ cudaError_t launch_precompute(const int32_t *parent, int n_trees, int n_nodes, i
 cudaError_t launch_pack(const int64_t *anc_idx, const uint8_t *anc_mask, const int64_t *leaf_idx,
                         int n_trees, int nb, int bm, int ma, int64_t index_base, void *packed,
                         size_t packed_stride, int32_t *status, cudaStream_t stream) {
+    const size_t smem = size_t(ma) * 4;
+    const int slot = current_device_slot();
+    if (slot < 0) return cudaErrorInvalidDevice;
+    if (smem > 48 * 1024 && smem > g_pack_smem_set[slot].load(std::memory_order_acquire)) {
+        cudaError_t e = cudaFuncSetAttribute(pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        g_pack_smem_set[slot].store(smem, std::memory_order_release);
+    }
     dim3 grid(nb, n_trees);
-    pack_kernel<<<grid, PACK_THREADS, size_t(ma) * 4, stream>>>(
+    pack_kernel<<<grid, PACK_THREADS, smem, stream>>>(
         anc_idx, anc_mask, leaf_idx, bm, ma, index_base, static_cast<unsigned char *>(packed),
         packed_stride, status);
     return cudaGetLastError();

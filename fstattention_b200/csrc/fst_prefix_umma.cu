@@ -496,19 +496,10 @@ prefix_umma_kernel(const AttnArgs a, const PrefixArgs pa, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
-// rank-4 map with 64-column x 128-row boxes
+// rank-4 map with 64-column x 128-row boxes (kept in the calling thread's table of maps)
 static bool make_map_rows128(CUtensorMap *map, const void *base, bool bf16, int D, int rows, int H, int Z,
                              int64_t stride_n, int64_t stride_h, int64_t stride_z) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return false;
-    const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(rows), cuuint64_t(H), cuuint64_t(Z)};
-    const cuuint64_t strides[3] = {cuuint64_t(stride_n) * 2, cuuint64_t(stride_h) * 2, cuuint64_t(stride_z) * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-              const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return make_map(map, base, bf16, D, rows, H, Z, stride_n, stride_h, stride_z, 128);
 }
 
 // rank-4 map over a page pool (columns, rows of a page, K/V heads, pages) with 64-column x page boxes
@@ -540,15 +531,12 @@ static cudaError_t launch_prefix_t(const AttnArgs &a, const PagedArgs *pg, int n
                !make_map_rows128(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z)) {
         return cudaErrorNotSupported;
     }
-    static bool configured_on[kMaxDevices] = {};
-    const int slot = current_device_slot();
-    if (slot < 0) return cudaErrorInvalidDevice;
-    if (!configured_on[slot]) {
-        cudaError_t e = cudaFuncSetAttribute(prefix_umma_kernel<T, D, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             umma::Geo<D>::SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-        configured_on[slot] = true;
-    }
+    static DeviceOnce configured;
+    const cudaError_t ce = configured.run([&] {
+        return cudaFuncSetAttribute(prefix_umma_kernel<T, D, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    umma::Geo<D>::SMEM_BYTES);
+    });
+    if (ce != cudaSuccess) return ce;
     if ((long long)a.Z * n_runs > 65535) return cudaErrorInvalidValue;
     PrefixArgs pa{n_runs, first_slot, nullptr, nullptr, 0, 0, 0};
     if (PAGED) {

@@ -114,13 +114,13 @@ cudaError_t launch_dfs_order(const int32_t *parent, int n_trees, int n_nodes, in
                              int32_t *new_parent, int32_t *status, cudaStream_t stream) {
     if (n_nodes > REORDER_MAX_NODES) return cudaErrorInvalidValue;
     const size_t smem = (size_t(n_nodes) * 4 + 1) * sizeof(int32_t);
-    static size_t enabled[kMaxDevices] = {};              // largest dynamic shared memory enabled, per device
+    static std::atomic<size_t> enabled[kMaxDevices];      // largest dynamic shared memory enabled, per device
     const int slot = current_device_slot();
     if (slot < 0) return cudaErrorInvalidDevice;
-    if (smem > 48 * 1024 && smem > enabled[slot]) {
+    if (smem > 48 * 1024 && smem > enabled[slot].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(dfs_order_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        enabled[slot] = smem;
+        enabled[slot].store(smem, std::memory_order_release);
     }
     dfs_order_kernel<<<n_trees, REORDER_THREADS, smem, stream>>>(parent, n_nodes, order, new_parent, status);
     return cudaGetLastError();

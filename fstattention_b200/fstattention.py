@@ -10,6 +10,7 @@ prefix every query attends to.  The launch is asynchronous on torch's current st
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -29,11 +30,32 @@ def _status_record(device) -> torch.Tensor:
     return rec
 
 
-def last_status(device=None) -> int:
-    """Device-side status code recorded by attention launches on ``device`` (synchronises)."""
+def _resolve(device) -> torch.device:
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    rec = _status.get(device)
-    return 0 if rec is None else int(rec[0].item())
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
+def last_status(device=None, clear: bool = False) -> int:
+    """Device-side status code recorded by attention launches on ``device`` (synchronises).
+
+    The record keeps the first problem it saw until it is cleared: pass ``clear=True`` (or call
+    ``clear_status``) once the code has been dealt with, so that later launches report afresh."""
+    rec = _status.get(_resolve(device))
+    if rec is None:
+        return 0
+    code = int(rec[0].item())
+    if clear and code != 0:
+        rec.zero_()
+    return code
+
+
+def clear_status(device=None) -> None:
+    """Zero the status record of ``device`` (asynchronous, on the current stream)."""
+    rec = _status.get(_resolve(device))
+    if rec is not None:
+        rec.zero_()
 
 
 def _strides(t):
@@ -158,6 +180,8 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     status = _status_record(dev)
     stream = _raw_stream(dev)
     kern = _lib.KERNELS[kernel]
+    if not math.isfinite(sm_scale):
+        raise ValueError("sm_scale must be finite")
     common_shape = [Z, H, n_q, n_kv, D] + _strides(q) + _strides(k) + _strides(v) + _strides(o)
 
     meta = ancestor_idx if isinstance(ancestor_idx, TreeMetadata) else \
@@ -173,6 +197,12 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
             if meta.n_blocks != -(-n_q // BLOCK_M):
                 raise ValueError("metadata block count does not match q")
             packed_ptr, packed_stride = meta.packed.data_ptr(), (meta.tree_stride if meta.n_trees > 1 else 0)
+            # From the second launch after the precompute on, the launch ahead of this one in
+            # the stream cannot be the metadata's writer: the kernel may then fetch its index
+            # lists while that launch drains (FST_KERNEL_FLAG_META_STABLE).
+            if meta.reads_since_build > 0:
+                kern |= _lib.KERNEL_FLAG_META_STABLE
+            meta.reads_since_build += 1
         else:
             # the reference's three tensors (fstattention.py:153): packed here, one more launch,
             # with the prefix length as index base (its test shifts the indices, sentinels included)

@@ -42,6 +42,9 @@ class TreeMetadata:
         self.ancestor_idx, self.ancestor_mask, self.leaf_idx = ancestor_idx, ancestor_mask, leaf_idx
         self.batched = batched
         self._versions = self._current_versions()
+        # attention launches that have read the packed form since it was last written: from the
+        # second one on, the launch ahead of the call in the stream cannot be the writer
+        self.reads_since_build = 0
 
     def _current_versions(self):
         return tuple(t._version if t is not None else -1
@@ -150,9 +153,65 @@ def build_tree_metadata(parent: TreeLike, block_m: int = 64, max_ancestors: int 
             torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(rc, "fst_precompute")
     meta._versions = meta._current_versions()
+    meta.reads_since_build = 0
     if check:
         meta.check()
     return meta
+
+
+def tree_topk_nodes(depth: int = 7, topk: int = 4, left_weight_factor: float = 0.5) -> int:
+    """Node count of the forest ``build_tree_topk`` / the reference's ``create_tree`` makes."""
+    n = int(_lib.lib().fst_tree_topk_nodes(depth, topk, float(left_weight_factor)))
+    if n < 0:
+        raise ValueError("forest shape beyond the kernel's limits (a level above 4096 nodes, or more than 32 levels)")
+    return n
+
+
+def build_tree_topk(scores: torch.Tensor, depth: Optional[int] = None, topk: Optional[int] = None,
+                    left_weight_factor: float = 0.5, max_nodes: Optional[int] = None, *,
+                    return_choice: bool = False, return_scores: bool = False):
+    """Grow the speculation tree on the GPU from the heads' top-k candidate scores.
+
+    ``scores`` is a CUDA float32 tensor ``[depth + 1, topk]`` (one tree) or ``[T, depth + 1, topk]``:
+    row ``l`` holds the scores (log-probabilities) of head ``l``'s ``topk`` candidates.  The
+    forest has the shape of the reference's ``create_tree(depth, topk, left_weight_factor)``
+    (utils.py:27-77) - ``topk`` roots, of every level the ``int(size * left_weight_factor)``
+    best-scoring nodes (score = sum along the path) expanded into the next head's candidates -
+    and with equal scores is exactly that forest.  Returns the parent array, int32 ``[N]`` /
+    ``[T, N]`` on the GPU (``N = max_nodes`` or the forest's node count), ready for
+    ``dfs_order_device`` / ``build_tree_metadata(parent, check=False)``; with ``return_choice``
+    also ``choice`` (``l * topk + k``: which candidate each node stands for) and with
+    ``return_scores`` the nodes' path scores.  One launch on the current stream, no host
+    synchronisation.
+    """
+    if not scores.is_cuda or scores.dtype != torch.float32 or scores.dim() not in (2, 3):
+        raise TypeError("scores must be a CUDA float32 tensor [depth + 1, topk] or [T, depth + 1, topk]")
+    batched = scores.dim() == 3
+    levels, k = scores.shape[-2:]
+    depth = levels - 1 if depth is None else depth
+    topk = k if topk is None else topk
+    if (depth + 1, topk) != (levels, k):
+        raise ValueError("scores must have depth + 1 rows of topk entries")
+    n_trees = scores.shape[0] if batched else 1
+    total = tree_topk_nodes(depth, topk, left_weight_factor)
+    n = total if max_nodes is None else int(max_nodes)
+    if n <= 0:
+        raise ValueError("max_nodes must be positive")
+    sc = scores.contiguous()
+    dev = sc.device
+    lead = (n_trees,) if batched else ()
+    parent = torch.empty(lead + (n,), dtype=torch.int32, device=dev)
+    choice = torch.empty(lead + (n,), dtype=torch.int32, device=dev) if return_choice else None
+    nscore = torch.empty(lead + (n,), dtype=torch.float32, device=dev) if return_scores else None
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fst_build_tree_topk(
+            sc.data_ptr(), n_trees, depth, topk, float(left_weight_factor), n, parent.data_ptr(),
+            choice.data_ptr() if choice is not None else None,
+            nscore.data_ptr() if nscore is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "fst_build_tree_topk")
+    extra = tuple(t for t in (choice, nscore) if t is not None)
+    return (parent,) + extra if extra else parent
 
 
 def parent_from_lineage(lineage: torch.Tensor, level_lookup: torch.Tensor) -> torch.Tensor:

@@ -2,8 +2,15 @@
  * fstattn_b200 - fused sparse tree attention for NVIDIA B200 (sm_100a), C ABI.
  *
  * Everything here is plain C: device pointers, sizes and a CUDA stream handle passed as
- * void*.  No function allocates, frees or synchronises; each one enqueues its kernels on the
- * given stream and returns a status code (0 = FST_OK) describing host-side argument checks.
+ * void*.  No function allocates or frees device memory or synchronises; each one enqueues its
+ * kernels on the given stream and returns a status code (0 = FST_OK) describing host-side
+ * argument checks.  Host-side state the library keeps: per host thread a table of the tensor
+ * maps it has built (about 200 KB of host memory, filled as calls come), and - only for calls
+ * that hand a shared prefix to the tcgen05 kernel (fst_attention_fwd_splitkv / _gqa / _paged with
+ * a workspace) - one extra CUDA stream and two events per host thread and device, created at the
+ * first such call outside stream capture and kept until the process ends.  The first call of a
+ * kernel variant on a device also sets that kernel's shared-memory attribute; make one call per
+ * shape and dtype before capturing a stream into a graph.
  * Problems that only the GPU can see (a malformed tree, too many ancestors in a block, an
  * index out of range) are recorded in a caller-provided device status record
  * (int32_t status[FST_STATUS_WORDS]) and never fault the device; the kernels keep going with
@@ -55,6 +62,18 @@ enum fst_kernel {
     FST_KERNEL_TMA_UMMA = 6        /* tree part as FST_KERNEL_TMA, shared prefix by the tcgen05  */
                                    /* kernel (head_dim 64 / 128, fst_attention_fwd_splitkv only) */
 };
+
+/*
+ * Flags that may be OR-ed into the `kernel` argument.
+ * FST_KERNEL_FLAG_META_STABLE: the packed metadata was completely written before the launch that
+ * precedes this call on the stream began (one precompute per decode step, then one attention call
+ * per layer: true for every call but the first after the precompute).  The tree kernel is
+ * launched so that it may become resident while the kernel ahead of it drains; with this flag it
+ * fetches its index list and mask words during that time instead of afterwards.  Q, K, V and O
+ * are never touched early.  Leaving the flag out is always correct.
+ */
+#define FST_KERNEL_MASK 0xff
+#define FST_KERNEL_FLAG_META_STABLE 0x100
 
 int fst_version(void);
 const char *fst_status_string(int status);
@@ -123,6 +142,32 @@ int fst_dfs_order(const int32_t *parent, int n_trees, int n_nodes, int32_t *orde
                   int32_t *new_parent, int32_t *status, void *stream);
 
 /*
+ * Tree construction on the device from top-k candidate scores.  The reference builds its forest
+ * on the CPU and only as a fixed synthetic shape (create_tree, utils.py:27-77: topk roots, level
+ * sizes size[l] = topk * int(size[l-1] * left_weight_factor), node r of a level under node
+ * r / topk of the level above); its README.md:17 names the use, Medusa-style trees over every
+ * head's top-k candidates.  Here the same recurrence is driven by scores so that a decode step
+ * never leaves the GPU (this call, then fst_dfs_order and/or fst_precompute):
+ *   scores     float [n_trees][depth + 1][topk]  candidate scores (log-probabilities) of head l
+ *   parent     int32 [n_trees][max_nodes]        out: parent[i] < i, -1 for the topk roots
+ *   choice     int32 [n_trees][max_nodes]        out, optional: l * topk + k, the candidate
+ *                                                 (head l, k-th entry of its scores) node i stands for
+ *   node_score float [n_trees][max_nodes]        out, optional: sum of the scores along the path
+ * A node's score is the sum along its path.  Of every level the int(size * left_weight_factor)
+ * best nodes are expanded, best first (ties: the earlier node), each into the topk candidates of
+ * the next head in the order given; nodes are numbered level by level.  With equal scores
+ * the parent array is exactly that of create_tree(depth, topk, left_weight_factor).  The node
+ * count depends on the three shape arguments only: fst_tree_topk_nodes() (-1: a level outgrows
+ * the kernel's 4096 nodes, or more than 32 levels).  Nodes at and beyond max_nodes are dropped;
+ * entries between the node count and max_nodes become isolated roots (parent -1, choice -1).
+ * Device pointers.
+ */
+long long fst_tree_topk_nodes(int depth, int topk, double left_weight_factor);
+int fst_build_tree_topk(const float *scores, int n_trees, int depth, int topk,
+                        double left_weight_factor, int max_nodes, int32_t *parent, int32_t *choice,
+                        float *node_score, void *stream);
+
+/*
  * Convert reference-format metadata (the three tensors of utils.py:104-129, already on the
  * device) into packed blobs.  index_base is subtracted from every index; entries below it
  * are padding.  The reference's test shifts the index tensors by the prefix length,
@@ -148,8 +193,10 @@ int fst_pack_metadata(const int64_t *ancestor_idx, const uint8_t *ancestor_mask,
  *          batch element z
  * The prefix length is n_kv - n_q, as in fstattention.py:163.  Block rows >= n_q are neither
  * read nor written, so n_q need not be a multiple of block_m.
- * dtype: FST_F16 / FST_BF16 (tensor cores, head_dim 64 or 128, block_m 16..128 multiple of
- * 16) or any of the three with head_dim in {16,32,64,128} on the fp32 SIMT kernel.
+ * dtype: FST_F16 / FST_BF16 (tensor cores: head_dim 64 or 128 and block_m 16, 32, 64 or 128;
+ * other block sizes run on the SIMT kernel) or any of the three with head_dim in {16,32,64,128}
+ * on the fp32 SIMT kernel.  sm_scale: any finite value of either sign, applied before the row
+ * maximum as in fstattention.py:78-97 (NaN or infinity: FST_ERR_INVALID_ARG).
  */
 int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse,
                       const void *packed, size_t meta_tree_stride,
@@ -272,8 +319,11 @@ int fst_attention_fwd_ref(const void *q, const void *k, const void *v, void *o, 
  *   - Metadata whose packed form (fst_attention_ref_workspace_bytes) exceeds
  *     FST_STATIC_SCRATCH_BYTES is refused with FST_ERR_TOO_LARGE and nothing is launched.
  *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress) with that device current; make that first call before any stream
- *     capture begins.  Later calls only launch kernels.  No call allocates or frees memory.
+ *     (cudaGetSymbolAddress) with that device current, and the first call with a new
+ *     combination of dtype, head_dim and block_m sets the shared-memory attribute of the kernel
+ *     it picks and builds its tensor maps (host memory only): make one call per such combination
+ *     before any stream capture begins.  Calls after that only launch kernels.  No call
+ *     allocates or frees device memory.
  *   - All calls on a device share the one array and it keeps whatever the last call wrote;
  *     every call rewrites all of it that it reads, so nothing has to be cleared.  Two calls
  *     whose kernels can overlap on the GPU (different streams without ordering) race on it:

@@ -101,7 +101,7 @@ def block_padded_mask(lineage: torch.Tensor, block_m: int) -> torch.Tensor:
 # block metadata                                                          (utils.py:104-129)
 # --------------------------------------------------------------------------------------------
 def block_metadata(lineage: torch.Tensor, level_lookup: torch.Tensor, block_m: int = 64,
-                   max_ancestors: int = 32):
+                   max_ancestors: int = 32, blocks: Sequence[int] | None = None):
     """Per query block: sorted unique ancestors, row-by-ancestor mask, leaf list.
 
     Returns ``(ancestor_idx [nb, MA] int64, ancestor_mask [nb, bm, MA] bool,
@@ -117,7 +117,9 @@ def block_metadata(lineage: torch.Tensor, level_lookup: torch.Tensor, block_m: i
         (utils.py:124-127).
 
     Unlike the reference this does not modify ``lineage`` (the reference writes each node into
-    its own lineage row, utils.py:124-125); the caller's tensor is left alone.
+    its own lineage row, utils.py:124-125); the caller's tensor is left alone.  ``blocks``
+    restricts the loop of utils.py:114 to the listed blocks (spot checks of very large trees);
+    the other blocks' entries keep their padding values.
     """
     n = lineage.shape[0]
     nb = math.ceil(n / block_m)
@@ -125,7 +127,7 @@ def block_metadata(lineage: torch.Tensor, level_lookup: torch.Tensor, block_m: i
     anc_mask = torch.zeros((nb, block_m, max_ancestors), dtype=torch.bool)
     leaf_idx = torch.full((nb, block_m), -1, dtype=torch.long)
     lin = lineage.clone()
-    for b in range(nb):
+    for b in (range(nb) if blocks is None else blocks):
         lo, hi = b * block_m, min((b + 1) * block_m, n)
         rows = lin[lo:hi]
         uniq = torch.unique(rows.reshape(-1))

@@ -568,3 +568,130 @@ def test_dfs_renumbering_leaves_the_result_unchanged(fst):
     assert maxabs(out.cpu(), exact) <= TOL_F16
     before = fst.build_tree_metadata(par, 64, 700)
     assert int(meta.packed.view(torch.int32)[0, :meta.n_blocks].sum()) < int(before.packed.view(torch.int32)[0, :before.n_blocks].sum())
+
+
+@pytest.mark.parametrize("scale", [-0.3, 0.0, -1.0 / 128 ** 0.5])
+def test_any_finite_scale_as_the_reference(fst, scale):
+    """The reference scales the scores before the row maximum (fstattention.py:78-97) and so takes
+    a factor of either sign; every kernel here must give the oracle's answer for it too, also
+    behind a prefix long enough for the split paths."""
+    from fstattention_b200 import configs
+    par = configs.random_window_tree(3, 200, 16)
+    n = len(par)
+    for dtype, d, bm, prefix in ((torch.float16, 128, 64, 0), (torch.float16, 64, 32, 300), (torch.float32, 32, 16, 7)):
+        q, k, v = make_qkv(1, 2, n, prefix + n, d, dtype, seed=21)
+        meta = fst.build_tree_metadata(par, bm, 64)
+        exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
+        tol = TOL_F32 if dtype == torch.float32 else TOL_F16
+        for kern in kernels_for(dtype, d, bm):
+            o, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern,
+                                       return_lse=True)
+            assert maxabs(o.cpu(), exact) <= tol, (scale, dtype, kern, maxabs(o.cpu(), exact))
+            assert torch.isfinite(lse).all()
+    q = torch.zeros((1, 1, n, 64), dtype=torch.float16, device="cuda")
+    for bad in (float("nan"), float("inf")):
+        with pytest.raises(ValueError, match="finite"):
+            fst.fst_attention(q, q, q, meta, sm_scale=bad)
+    # the C entry point refuses it as well
+    from fstattention_b200 import _lib
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    rc = _lib.lib().fst_attention_fwd(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), None,
+                                      meta.packed.data_ptr(), 0, 1, 1, n, n, 64, *q.stride()[:3], *q.stride()[:3],
+                                      *q.stride()[:3], *q.stride()[:3], 16, 64, float("nan"), 0, 0, st.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 1
+    assert fst.last_status() == 0
+
+
+def test_status_record_can_be_cleared(fst):
+    """One recorded problem must not stick for the life of the process."""
+    par = [-1, 0, 0, 1]
+    meta = fst.build_tree_metadata(par, 16, 16)
+    q = torch.randn(1, 1, 4, 64).half().cuda()
+    fst.fst_attention(q, q, q, meta, sm_scale=1.0)
+    assert fst.last_status() == 0
+    # metadata that points past the K/V rows: recorded, not a fault
+    ai, am, li = (t.clone() for t in meta)
+    ai[0, 0] = 99
+    am[0, 3, 0] = True
+    fst.fst_attention(q, q, q, ai, am, li, 1.0, BLOCK_M=16, MAX_ANCESTORS=16)
+    assert fst.last_status() == 18                      # FST_DEV_INDEX_RANGE
+    assert fst.last_status(clear=True) == 18
+    assert fst.last_status() == 0
+    fst.fst_attention(q, q, q, ai, am, li, 1.0, BLOCK_M=16, MAX_ANCESTORS=16)
+    assert fst.last_status() == 18
+    fst.clear_status()
+    o = fst.fst_attention(q, q, q, meta, sm_scale=1.0)
+    assert fst.last_status() == 0 and torch.isfinite(o).all()
+
+
+def test_metadata_fetched_ahead_of_the_dependency_wait(fst):
+    """From the second call after a precompute on, the Python layer lets the kernel read its index
+    lists before it waits for the launch ahead of it.  Results must not depend on that: a run of
+    back-to-back layers, eagerly and as a replayed CUDA graph with the tree changing between
+    replays, against calls that each follow their own precompute."""
+    from fstattention_b200 import configs, _lib
+    trees = [configs.random_window_tree(s, 512, 48) for s in range(4)]
+    H, D, n = 8, 128, 512
+    layers = [tuple(x.cuda() for x in make_qkv(1, H, n, n, D, torch.float16, seed=40 + i)) for i in range(6)]
+    parent = torch.tensor(trees[0], dtype=torch.int32, device="cuda")
+    meta = fst.build_tree_metadata(parent, 64, 320, reference_format=False)
+    outs = [torch.empty_like(l[0]) for l in layers]
+
+    def step():
+        fst.build_tree_metadata(parent, 64, 320, out=meta, check=False)
+        for (q, k, v), o in zip(layers, outs):
+            fst.fst_attention(q, k, v, meta, sm_scale=D ** -0.5, out=o)
+
+    step()
+    assert meta.reads_since_build == len(layers)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for t, par in enumerate(trees):
+        parent.copy_(torch.tensor(par, dtype=torch.int32))
+        graph.replay()
+        torch.cuda.synchronize()
+        fresh = fst.build_tree_metadata(par, 64, 320, reference_format=False)
+        for (q, k, v), o in zip(layers, outs):
+            fresh.reads_since_build = 0                   # every call as the first after its precompute
+            want = fst.fst_attention(q, k, v, fresh, sm_scale=D ** -0.5)
+            assert torch.equal(o, want), t
+    exact = oracle_attention(*(x.cpu() for x in layers[-1]), trees[-1], D ** -0.5, compute_dtype=torch.float32, head_chunk=2)
+    assert maxabs(outs[-1].cpu(), exact) <= TOL_F16
+    assert fst.last_status() == 0
+
+
+def test_forest64_full_size_against_the_oracle(fst):
+    """All 64 trees x 32 heads of the batched configuration, dense oracle tree by tree."""
+    from fstattention_b200 import configs
+    w = configs.workload("forest64")
+    T, H, n, D = len(w.trees), w.heads, w.n_nodes, w.head_dim
+    q, k, v = make_qkv(T, H, n, n, D, torch.float16, seed=61)
+    meta = fst.build_tree_metadata(w.trees, w.block_m, w.max_ancestors, reference_format=False)
+    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale).cpu()
+    worst = 0.0
+    for t in range(T):
+        exact = oracle_attention(q[t:t + 1], k[t:t + 1], v[t:t + 1], w.trees[t], w.sm_scale,
+                                 compute_dtype=torch.float32)
+        worst = max(worst, maxabs(o[t:t + 1], exact))
+    assert worst <= TOL_F16, worst
+    assert fst.last_status() == 0
+
+
+def test_deep4096_all_heads_row_slices_against_the_oracle(fst):
+    """The deep tree at its full head count: every head, the query rows of the first, a middle and
+    the last two blocks against the dense oracle."""
+    from fstattention_b200 import configs
+    w = configs.workload("deep4096")
+    H, n, D = w.heads, w.n_nodes, w.head_dim
+    q, k, v = make_qkv(1, H, n, n, D, torch.float16, seed=62)
+    meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors, reference_format=False)
+    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale).cpu()
+    lin, _ = orc.lineage_from_parent(w.trees[0])
+    mask = orc.full_attention_mask(lin, pad_rows=0)
+    rows = torch.cat([torch.arange(0, 64), torch.arange(2048, 2112), torch.arange(n - 128, n)])
+    exact = orc.dense_tree_attention(q[:, :, rows], k, v, mask[rows], w.sm_scale, torch.float32, head_chunk=8)
+    assert maxabs(o[:, :, rows], exact) <= TOL_F16
+    assert fst.last_status() == 0

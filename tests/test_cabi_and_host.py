@@ -29,7 +29,8 @@ def test_bindings_match_the_header(built_lib):
     code = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
     from fstattention_b200 import _lib
     lib = _lib.lib()
-    kinds = {"int": C.c_int, "int64_t": C.c_int64, "size_t": C.c_size_t, "float": C.c_float}
+    kinds = {"int": C.c_int, "int64_t": C.c_int64, "size_t": C.c_size_t, "float": C.c_float,
+             "double": C.c_double}
     for name, params in re.findall(r"\b(fst_[a-z_0-9]+)\s*\(([^)]*)\)\s*;", code):
         params = params.strip()
         want = []

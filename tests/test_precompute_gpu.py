@@ -219,3 +219,112 @@ def test_dfs_order_device_batch_and_errors(fst):
     with pytest.raises(RuntimeError):
         fst.dfs_order_device([-1] + [0] * 8192)              # more nodes than the kernel holds
 
+
+
+def test_reference_largest_context_131068_nodes(fst):
+    """The largest tree of the reference's own tables (DEPTH_MAPPING[2**17] = 14, utils.py:4-13:
+    131068 nodes), block 128, 64 ancestors: sampled blocks against the oracle, bit for bit."""
+    lin, lvl = fst.create_tree(14)
+    par = fst.parent_from_lineage(lin, lvl)
+    n, bm, ma = par.shape[0], 128, 64
+    assert n == 2 ** 17 - 4
+    meta = fst.build_tree_metadata(par.to(torch.int32), bm, ma)
+    nb = meta.n_blocks
+    blocks = [0, 1, 2, 17, 255, 256, 511, nb // 2, nb - 2, nb - 1]
+    ai, am, li = orc.block_metadata(lin, lvl, bm, ma, blocks=blocks)
+    g_ai, g_am, g_li = (t.cpu() for t in meta)
+    for b in blocks:
+        assert torch.equal(g_ai[b], ai[b]), b
+        assert torch.equal(g_am[b], am[b]), b
+        assert torch.equal(g_li[b], li[b]), b
+    # the documented node limit itself: segments of 4096 nodes whose first 64 are roots and whose
+    # other nodes hang under one of them, so that ancestors sit at high node numbers
+    n2 = 262144
+    i = torch.arange(n2)
+    par2 = torch.where(i % 4096 < 64, torch.full_like(i, -1), i // 4096 * 4096 + i % 64).to(torch.int32)
+    meta2 = fst.build_tree_metadata(par2, 256, 128)
+    cnt = meta2.packed.cpu().numpy()[0, : meta2.n_blocks * 4].view(np.int32)
+    a2 = meta2.ancestor_idx.cpu()
+    for b in (0, 1, 500, meta2.n_blocks - 1):
+        lo = b * 256
+        want = sorted({x for k in range(lo, lo + 256) for x in _ancestors(par2, k)})
+        got = [int(x) for x in a2[b] if x >= 0]
+        assert got == want, b
+        assert cnt[b] == sum(1 for x in want if x < lo)
+
+
+def _ancestors(par, k):
+    out = []
+    x = int(par[k])
+    while x >= 0:
+        out.append(x)
+        x = int(par[x])
+    return out
+
+
+def test_size_that_does_not_fit_is_refused(fst):
+    """block_m 1024 at the full node count needs more shared memory than an SM has: a clear
+    status, not a launch failure."""
+    from fstattention_b200 import _lib
+    par = torch.full((262144,), -1, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="beyond the supported limit"):
+        fst.build_tree_metadata(par, 1024, 2048, reference_format=False)
+    torch.cuda.synchronize()
+
+
+def _topk_forest_cpu(scores, topk, lwf):
+    """The construction build_tree_topk documents, with a stable sort on the CPU."""
+    levels = scores.shape[0]
+    parent, choice, cum = [-1] * topk, list(range(topk)), [list(map(float, scores[0]))]
+    start = [0, topk]
+    for l in range(1, levels):
+        prev = np.array(cum[-1], dtype=np.float32)
+        keep = int(len(prev) * lwf)
+        order = np.argsort(-prev, kind="stable")[:keep]
+        nxt = []
+        for p in order:
+            for k in range(topk):
+                parent.append(start[l - 1] + int(p))
+                choice.append(l * topk + k)
+                nxt.append(np.float32(prev[p] + np.float32(scores[l, k])))
+        cum.append(nxt)
+        start.append(start[-1] + len(nxt))
+    return parent, choice, [x for lvl in cum for x in lvl]
+
+
+@pytest.mark.parametrize("depth,topk,lwf", [(7, 4, 0.5), (5, 10, 0.3), (9, 4, 0.5), (3, 3, 1.0)])
+def test_device_built_tree_equals_create_tree_on_equal_scores(fst, depth, topk, lwf):
+    lin, lvl = fst.create_tree(depth, topk, lwf)
+    want = fst.parent_from_lineage(lin, lvl)
+    scores = torch.zeros((depth + 1, topk), dtype=torch.float32, device="cuda")
+    got = fst.build_tree_topk(scores, left_weight_factor=lwf)
+    assert got.dtype == torch.int32 and got.shape == want.shape
+    assert torch.equal(got.cpu().long(), want)
+    assert fst.tree_topk_nodes(depth, topk, lwf) == want.shape[0]
+
+
+def test_device_built_tree_follows_the_scores(fst):
+    g = torch.Generator().manual_seed(8)
+    depth, topk, lwf, T = 6, 4, 0.5, 5
+    scores = torch.log_softmax(torch.randn((T, depth + 1, topk), generator=g), dim=-1)
+    scores[1, 2] = scores[1, 2, 0]                       # a level of ties in one tree
+    n = fst.tree_topk_nodes(depth, topk, lwf)
+    parent, choice, nscore = fst.build_tree_topk(scores.cuda(), left_weight_factor=lwf, max_nodes=n + 12,
+                                                 return_choice=True, return_scores=True)
+    for t in range(T):
+        wp, wc, ws = _topk_forest_cpu(scores[t].numpy(), topk, lwf)
+        assert parent[t, :n].cpu().tolist() == wp, t
+        assert choice[t, :n].cpu().tolist() == wc, t
+        assert np.allclose(nscore[t, :n].cpu().numpy(), np.array(ws, dtype=np.float32), rtol=0, atol=1e-5)
+        assert parent[t, n:].cpu().tolist() == [-1] * 12 and choice[t, n:].cpu().tolist() == [-1] * 12
+    # cut by a node budget: the first max_nodes nodes of the same forest
+    cut = fst.build_tree_topk(scores.cuda(), left_weight_factor=lwf, max_nodes=200)
+    assert torch.equal(cut, parent[:, :200])
+    # straight into the renumbering and the precompute, no host round trip
+    order, new_parent = fst.dfs_order_device(parent[0, :n], check=False)
+    meta = fst.build_tree_metadata(new_parent, 64, 64)
+    want = orc.block_metadata_from_parent(new_parent.cpu().tolist(), 64, 64)
+    for a, b in zip(meta, want):
+        assert torch.equal(a.cpu(), b)
+    with pytest.raises(ValueError, match="limits"):
+        fst.tree_topk_nodes(14, 4, 0.5)                  # a level of 32768 nodes
