@@ -233,7 +233,9 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     a.vs_z = v_stride_z; a.vs_h = v_stride_h; a.vs_n = v_stride_n;
     a.os_z = o_stride_z; a.os_h = o_stride_h; a.os_n = o_stride_n;
     a.bm = block_m; a.ma = max_ancestors; a.nb = (n_q + block_m - 1) / block_m;
-    a.scale_log2 = sm_scale * 1.4426950408889634f;
+    // A factor of zero would turn the -inf of a masked score into NaN inside the exponent's
+    // multiply-add; a factor too small to move any finite score gives the same uniform weights.
+    a.scale_log2 = sm_scale == 0.f ? 1e-30f : sm_scale * 1.4426950408889634f;
     a.status = status;
     a.n_splits = 1;
     a.part_o = nullptr;
@@ -256,14 +258,14 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (automatic)
         choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_TMA : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice < FST_KERNEL_MMA || choice > FST_KERNEL_TMA_UMMA) return FST_ERR_INVALID_ARG;
+    if (choice < FST_KERNEL_MMA || choice > FST_KERNEL_PERSIST) return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
 
     // A shared prefix with a workspace: either the tcgen05 prefix kernel takes it in kv_splits runs
     // while the tree kernel does the tree part (head_dim 64 or 128; chosen automatically from 256
     // prefix rows on), or the tree kernel itself is launched kv_splits times over the prefix.
-    const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA;
+    const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA && choice != FST_KERNEL_PERSIST;
     // (the tcgen05 kernel takes Q from shared memory as it arrived, so it cannot flip Q's sign
     // for a negative factor; the tree kernel walks the prefix itself then)
     const bool want_umma = can_part && (head_dim == 128 || head_dim == 64) && sm_scale > 0.f &&

@@ -33,12 +33,16 @@ def local_slice(t: torch.Tensor, axis: str, world: int, rank: int) -> torch.Tens
     return t.narrow(dim, lo, hi - lo)
 
 
-def all_gather_outputs(o_local: torch.Tensor, axis: str, n_total: int, group=None) -> torch.Tensor:
+def all_gather_outputs(o_local: torch.Tensor, axis: str, n_total: int, group=None, *,
+                       out: Optional[torch.Tensor] = None, async_op: bool = False):
     """Reassemble the full output from every rank's shard along ``axis``.
 
     Equal shards that are contiguous in the full tensor (tree axis, or head axis with Z == 1)
-    are gathered in place into one buffer; otherwise shards are padded to the largest one,
-    gathered and trimmed.
+    are gathered in place into one buffer (``out`` when given: nothing is allocated then);
+    otherwise shards are padded to the largest one, gathered and trimmed.  With ``async_op``
+    (in-place case only) the collective is enqueued behind the work already on the current
+    stream and ``(full, work)`` is returned at once: the caller goes on launching the next
+    layer's attention and calls ``work.wait()`` before it reads ``full``.
     """
     world = dist.get_world_size(group)
     dim = AXES[axis]
@@ -48,28 +52,41 @@ def all_gather_outputs(o_local: torch.Tensor, axis: str, n_total: int, group=Non
     full_shape = list(o_local.shape)
     full_shape[dim] = n_total
     in_place = len(set(sizes)) == 1 and (dim == 0 or o_local.shape[0] == 1)
+    if out is not None and (list(out.shape) != full_shape or out.dtype != o_local.dtype or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous tensor of the full shape")
     if in_place:
-        full = torch.empty(full_shape, dtype=o_local.dtype, device=o_local.device)
-        dist.all_gather_into_tensor(full.view(-1), o_local.contiguous().view(-1), group=group)
-        return full
+        full = torch.empty(full_shape, dtype=o_local.dtype, device=o_local.device) if out is None else out
+        work = dist.all_gather_into_tensor(full.view(-1), o_local.contiguous().view(-1), group=group,
+                                           async_op=async_op)
+        return (full, work) if async_op else full
+    if async_op:
+        raise ValueError("async_op needs equal shards that are contiguous in the full tensor")
     pad_shape = list(o_local.shape)
     pad_shape[dim] = max(sizes)
     padded = torch.zeros(pad_shape, dtype=o_local.dtype, device=o_local.device)
     padded.narrow(dim, 0, o_local.shape[dim]).copy_(o_local)
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
-    return torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
+    full = torch.cat([p.narrow(dim, 0, s) for p, s in zip(parts, sizes)], dim=dim)
+    if out is not None:
+        out.copy_(full)
+        return out
+    return full
 
 
 def sharded_fst_attention(q_local, k_local, v_local, meta_local, sm_scale: float, axis: str,
                           n_total: int, *, group=None, gather: bool = True,
-                          attention: Optional[Callable] = None, **kwargs) -> torch.Tensor:
+                          gathered: Optional[torch.Tensor] = None, async_gather: bool = False,
+                          attention: Optional[Callable] = None, **kwargs):
     """Tree attention on this rank's shard, then (optionally) the all-gather of outputs.
 
     ``axis="tree"``: the tensors hold this rank's trees (batch elements) and ``meta_local``
     their metadata.  ``axis="head"``: the tensors hold this rank's heads of every batch element
     and ``meta_local`` is the full tree metadata, identical on all ranks.  ``n_total`` is the
-    global number of trees or heads.
+    global number of trees or heads.  ``gathered`` receives the full output (no allocation);
+    ``async_gather`` returns ``(full, work)`` with the collective still under way, so that the
+    next layer's attention overlaps it (``work.wait()`` before reading ``full``).  Other keyword
+    arguments (``out=``, ``kernel=`` ...) go to ``fst_attention``.
     """
     if axis not in AXES:
         raise ValueError("axis must be 'tree' or 'head'")
@@ -78,4 +95,4 @@ def sharded_fst_attention(q_local, k_local, v_local, meta_local, sm_scale: float
     o_local = attention(q_local, k_local, v_local, meta_local, sm_scale=sm_scale, **kwargs)
     if not gather or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return o_local
-    return all_gather_outputs(o_local, axis, n_total, group)
+    return all_gather_outputs(o_local, axis, n_total, group, out=gathered, async_op=async_gather)

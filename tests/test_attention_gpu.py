@@ -27,10 +27,12 @@ def fst(built_lib):
     return fstattention_b200
 
 
-def kernels_for(dtype, d, bm):
+def kernels_for(dtype, d, bm, prefix=0):
     ks = ["auto", "simt"]
     if dtype in (torch.float16, torch.bfloat16) and d in (64, 128) and bm in (16, 32, 64, 128):
         ks += ["mma"] + (["tma_t32", "tma_t64"] if bm >= 32 else [])
+        if bm in (64, 128) and prefix == 0:              # the persistent kernel: no shared prefix
+            ks.append("persist")
     return ks
 
 
@@ -51,7 +53,7 @@ def test_golden_cases_all_kernels(fst, attention_golden):
         exact64 = orc.tree_attention_reference(q, k, v, par, scale, bm, prefix, torch.float64)[:, :, :n]
         noise = maxabs(dense, exact64)
         tol = TOL_F32 if q.dtype == torch.float32 else TOL_F16
-        for kern in kernels_for(q.dtype, q.shape[-1], bm):
+        for kern in kernels_for(q.dtype, q.shape[-1], bm, prefix):
             o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern)
             o = o.cpu()[:, :, :n]
             assert torch.isfinite(o).all(), (name, kern)
@@ -136,7 +138,7 @@ def test_full_size_equal_scores_property(fst, name):
     q = torch.randn((T, H, n, D), generator=g).half()
     k = torch.zeros_like(v)
     meta = fst.build_tree_metadata(w.trees if T > 1 else w.trees[0], w.block_m, w.max_ancestors)
-    for kern in ("mma", "tma_t32", "tma_t64"):
+    for kern in ("mma", "tma_t32", "tma_t64", "persist"):
         o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
         for t in range(0, T, 9):
             want = chain_mean_values(w.trees[t], v[t].double().numpy())
@@ -156,7 +158,7 @@ def test_full_size_kernels_agree(fst):
     q, k, v = (x.cuda() for x in make_qkv(1, w.heads, w.n_nodes, w.n_nodes, w.head_dim, torch.float16, 17))
     meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors)
     base = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel="simt")
-    for kern in ("mma", "tma_t32", "tma_t64"):
+    for kern in ("mma", "tma_t32", "tma_t64", "persist"):
         o = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel=kern)
         assert maxabs(o, base) <= TOL_F16, kern
 
@@ -176,7 +178,7 @@ def test_shapes_dtypes_and_prefix(fst, dtype, d, bm, prefix):
     scale = d ** -0.5
     exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
     tol = {torch.float16: TOL_F16, torch.bfloat16: TOL_BF16, torch.float32: TOL_F32}[dtype]
-    for kern in kernels_for(dtype, d, bm):
+    for kern in kernels_for(dtype, d, bm, prefix):
         o, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern,
                                    return_lse=True)
         assert maxabs(o.cpu(), exact) <= tol, (kern, maxabs(o.cpu(), exact))
@@ -580,10 +582,10 @@ def test_any_finite_scale_as_the_reference(fst, scale):
     n = len(par)
     for dtype, d, bm, prefix in ((torch.float16, 128, 64, 0), (torch.float16, 64, 32, 300), (torch.float32, 32, 16, 7)):
         q, k, v = make_qkv(1, 2, n, prefix + n, d, dtype, seed=21)
-        meta = fst.build_tree_metadata(par, bm, 64)
+        meta = fst.build_tree_metadata(par, bm, 128)
         exact = oracle_attention(q, k, v, par, scale, prefix=prefix, compute_dtype=torch.float32)
         tol = TOL_F32 if dtype == torch.float32 else TOL_F16
-        for kern in kernels_for(dtype, d, bm):
+        for kern in kernels_for(dtype, d, bm, prefix):
             o, lse = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=scale, kernel=kern,
                                        return_lse=True)
             assert maxabs(o.cpu(), exact) <= tol, (scale, dtype, kern, maxabs(o.cpu(), exact))
@@ -597,7 +599,7 @@ def test_any_finite_scale_as_the_reference(fst, scale):
     st = torch.zeros(4, dtype=torch.int32, device="cuda")
     rc = _lib.lib().fst_attention_fwd(q.data_ptr(), q.data_ptr(), q.data_ptr(), q.data_ptr(), None,
                                       meta.packed.data_ptr(), 0, 1, 1, n, n, 64, *q.stride()[:3], *q.stride()[:3],
-                                      *q.stride()[:3], *q.stride()[:3], 16, 64, float("nan"), 0, 0, st.data_ptr(),
+                                      *q.stride()[:3], *q.stride()[:3], 16, 128, float("nan"), 0, 0, st.data_ptr(),
                                       torch.cuda.current_stream().cuda_stream)
     assert rc == 1
     assert fst.last_status() == 0
@@ -670,13 +672,15 @@ def test_forest64_full_size_against_the_oracle(fst):
     T, H, n, D = len(w.trees), w.heads, w.n_nodes, w.head_dim
     q, k, v = make_qkv(T, H, n, n, D, torch.float16, seed=61)
     meta = fst.build_tree_metadata(w.trees, w.block_m, w.max_ancestors, reference_format=False)
-    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale).cpu()
-    worst = 0.0
+    outs = {kern: fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
+            for kern in ("auto", "tma_t32", "persist")}
+    worst = dict.fromkeys(outs, 0.0)
     for t in range(T):
         exact = oracle_attention(q[t:t + 1], k[t:t + 1], v[t:t + 1], w.trees[t], w.sm_scale,
                                  compute_dtype=torch.float32)
-        worst = max(worst, maxabs(o[t:t + 1], exact))
-    assert worst <= TOL_F16, worst
+        for kern, o in outs.items():
+            worst[kern] = max(worst[kern], maxabs(o[t:t + 1], exact))
+    assert max(worst.values()) <= TOL_F16, worst
     assert fst.last_status() == 0
 
 
@@ -688,10 +692,11 @@ def test_deep4096_all_heads_row_slices_against_the_oracle(fst):
     H, n, D = w.heads, w.n_nodes, w.head_dim
     q, k, v = make_qkv(1, H, n, n, D, torch.float16, seed=62)
     meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors, reference_format=False)
-    o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale).cpu()
     lin, _ = orc.lineage_from_parent(w.trees[0])
     mask = orc.full_attention_mask(lin, pad_rows=0)
     rows = torch.cat([torch.arange(0, 64), torch.arange(2048, 2112), torch.arange(n - 128, n)])
     exact = orc.dense_tree_attention(q[:, :, rows], k, v, mask[rows], w.sm_scale, torch.float32, head_chunk=8)
-    assert maxabs(o[:, :, rows], exact) <= TOL_F16
+    for kern in ("auto", "persist"):
+        o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
+        assert maxabs(o[:, :, rows], exact) <= TOL_F16, kern
     assert fst.last_status() == 0

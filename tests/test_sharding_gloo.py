@@ -56,6 +56,19 @@ def _worker(rank, world, port, axis, n_trees, heads, result_dir):
         local_only = sharding.sharded_fst_attention(ql, kl, vl, meta, 0.25, axis, total, gather=False,
                                                     attention=lambda a, b, c, m, sm_scale: _oracle_attention(a, b, c, m, sm_scale))
         assert torch.equal(local_only, sharding.local_slice(full, axis, world, rank))
+        # into a caller's buffer; and, where the shards are equal and contiguous in the full
+        # tensor, with the collective returned still under way
+        buf = torch.empty_like(full)
+        inject = lambda a, b, c, m, sm_scale: _oracle_attention(a, b, c, m, sm_scale)
+        if total % world == 0 and (axis == "tree" or n_trees == 1):
+            got2, work = sharding.sharded_fst_attention(ql, kl, vl, meta, 0.25, axis, total, gathered=buf,
+                                                        async_gather=True, attention=inject)
+            work.wait()
+        else:
+            got2 = sharding.sharded_fst_attention(ql, kl, vl, meta, 0.25, axis, total, gathered=buf, attention=inject)
+            with pytest.raises(ValueError):
+                sharding.all_gather_outputs(local_only, axis, total, async_op=True)
+        assert got2 is buf and torch.equal(buf, full)
         open(os.path.join(result_dir, f"ok_{axis}_{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
