@@ -392,6 +392,36 @@ def measure_case(fst, w, layers_n, reps, dev, kernel="auto", case=None):
     return out
 
 
+def measure_tree_build(fst, dev, reps):
+    """A decode step that grows its tree on the GPU: top-k scores -> parent array -> block
+    metadata, nothing crossing to the host (1020 nodes: the reference's create_tree(7) shape)."""
+    depth, topk, lwf = 7, 4, 0.5
+    g = torch.Generator(device=dev).manual_seed(3)
+    scores = torch.log_softmax(torch.randn((depth + 1, topk), generator=g, device=dev), dim=-1)
+    n = fst.tree_topk_nodes(depth, topk, lwf)
+    parent = fst.build_tree_topk(scores, left_weight_factor=lwf)
+    meta = fst.build_tree_metadata(parent, 64, 128, reference_format=False)
+
+    def build_only():
+        for _ in range(8):
+            fst.build_tree_topk(scores, left_weight_factor=lwf)
+
+    def build_and_precompute():
+        for _ in range(8):
+            par = fst.build_tree_topk(scores, left_weight_factor=lwf)
+            fst.build_tree_metadata(par, 64, 128, out=meta, check=False)
+
+    timer = Timer(dev, 1)
+    out = {"nodes": n, "depth": depth, "topk": topk, "left_weight_factor": lwf, "block_m": 64}
+    for key, fn in (("build_us", build_only), ("build_plus_precompute_us", build_and_precompute)):
+        graph = capture(fn)
+        for _ in range(3):
+            graph.replay()
+        out[key] = timer(graph.replay, reps) / reps / 8 * 1e3
+    assert meta.check() is meta
+    return out
+
+
 def seeded_full(shape, seed, dev, dtype):
     g = torch.Generator(device=dev).manual_seed(seed)
     return torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(dtype)
@@ -790,6 +820,7 @@ def run_ours(args, rank, world):
                 "deep4096": measure_case(fst, deep, 3, reps, dev, args.kernel),
                 "deep4096_bm128": measure_case(fst, with_block(deep, 128, 256), 3, reps, dev, args.kernel,
                                                case="deep4096_bm128"),
+                "device_built_tree": measure_tree_build(fst, dev, reps),
             }
         sharded = {name: measure_sharded(fst, name, rank, world, dev, 4, reps, args.kernel)
                    for name in ("forest64", "deep4096")}

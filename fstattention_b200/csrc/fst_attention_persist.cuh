@@ -444,12 +444,13 @@ cudaError_t launch_persist_d(const AttnArgs &a, cudaStream_t stream) {
     return cudaErrorNotSupported;
 }
 
-// The automatic choice takes this kernel when the items outnumber its resident CTAs several
-// times over (measured: below that the one-CTA-per-item kernel's finer balance wins).
-inline bool persist_pays(const AttnArgs &a) {
-    if (a.prefix != 0 || a.n_splits != 1 || a.skip_prefix || (a.bm != 64 && a.bm != 128)) return false;
-    const long long items = (long long)a.nb * a.H * a.Z;
-    return items >= 8LL * sm_count() * (a.bm <= 64 ? 2 : 1);
-}
+// Whether the automatic choice should take this kernel.  Measured on B200 (D 128, 64-row
+// blocks, fp16): 64 batched 256-node trees 171 us against 113 us for attn_tma_kernel, the deep
+// 4096-node tree 105 against 85 us - it loses.  The tree kernel is bound by how many warps with
+// dependent instruction chains an SM can interleave, and that is bound by registers: twelve
+// compute warps of 168 registers fill the register file, and this design spends two of its ten
+// warps per SM (and a third of the shared memory a third CTA would need) on staging.  So it is
+// never picked automatically; FST_KERNEL_PERSIST selects it by hand.
+inline bool persist_pays(const AttnArgs &) { return false; }
 
 }  // namespace fst

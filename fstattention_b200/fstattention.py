@@ -131,14 +131,8 @@ def launch_plan(q, prefix, block_m, kernel: str = "auto", kv_splits: Optional[in
         and block_m in (16, 32, 64, 128)
     tree = "attn_simt_kernel" if kernel == "simt" or not tensor_core else \
         "attn_mma_kernel" if kernel == "mma" or block_m == 16 else "attn_tma_kernel"
-    if tree == "attn_tma_kernel" and prefix == 0 and block_m in (64, 128):
-        # many (block, head, tree) items per SM: the persistent kernel (persist_pays in the library)
-        sms = _SMS.get(q.device)
-        if sms is None:
-            sms = _SMS[q.device] = torch.cuda.get_device_properties(q.device).multi_processor_count
-        items = q.shape[0] * q.shape[1] * -(-q.shape[2] // block_m)
-        if kernel == "persist" or (kernel in ("auto", "tma") and items >= 8 * sms * (2 if block_m == 64 else 1)):
-            tree = "attn_persist_kernel"
+    if kernel == "persist" and tree == "attn_tma_kernel" and prefix == 0 and block_m in (64, 128):
+        tree = "attn_persist_kernel"                      # by hand only: it measured slower than attn_tma_kernel
     if need_ws and q.shape[-1] in (64, 128) and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
         return {"kernels": ["prefix_umma_kernel", tree, "combine_splits_kernel"], "prefix_runs": splits}
     if need_ws:

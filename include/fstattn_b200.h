@@ -56,15 +56,15 @@ enum fst_kernel {
     FST_KERNEL_SIMT = 1,           /* fp32 arithmetic, any dtype / head_dim in {16,32,64,128}   */
     FST_KERNEL_MMA = 2,            /* tensor-core kernel, cp.async gathers: fp16/bf16, D 64/128  */
     FST_KERNEL_TMA = 3,            /* same arithmetic, TMA tile loads + mbarriers, swizzled smem; */
-                                   /* 32- or 64-column tiles, or FST_KERNEL_PERSIST, by grid size */
+                                   /* 32- or 64-column tiles chosen by grid size                 */
     FST_KERNEL_TMA_T32 = 4,        /* ... forced 32-column tiles (three CTAs per SM)             */
     FST_KERNEL_TMA_T64 = 5,        /* ... forced 64-column tiles (fewest softmax rounds)         */
     FST_KERNEL_TMA_UMMA = 6,       /* tree part as FST_KERNEL_TMA, shared prefix by the tcgen05  */
                                    /* kernel (head_dim 64 / 128, fst_attention_fwd_splitkv only) */
     FST_KERNEL_PERSIST = 7         /* persistent CTAs, a producer warp streaming tiles through a */
                                    /* shared-memory ring ahead of the arithmetic: block_m 64 or  */
-                                   /* 128, no prefix; what FST_KERNEL_AUTO / _TMA pick when the  */
-                                   /* (block, head, tree) items outnumber the SMs many times     */
+                                   /* 128, no prefix.  Slower than FST_KERNEL_TMA on every shape */
+                                   /* measured, so never the automatic choice                    */
 };
 
 /*
