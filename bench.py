@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument("--workload", default="medusa256")
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--kernel", default="auto")
+    ap.add_argument("--block-m", type=int, default=None, help="override the workload's query block size")
+    ap.add_argument("--max-ancestors", type=int, default=None, help="override the workload's ancestor bound")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="skip the workloads / sharded sub-objects")
@@ -478,6 +480,18 @@ def measure_sharded(fst, name, rank, world, dev, layers_n, reps, kernel="auto"):
         for work in works:
             work.wait()
 
+    shared = None
+    if world > 1:
+        try:                                              # one shared full tensor per layer, every rank's copy mapped everywhere
+            shared = [sharding.GatheredOutput(full_shape, dtype, dev) for _ in range(layers_n)]
+        except Exception as exc:                          # noqa: BLE001
+            shared = f"{type(exc).__name__}: {exc}"[:300]
+
+    def step_fused():
+        fst.build_tree_metadata(parent, w.block_m, w.max_ancestors, out=meta, check=False)
+        for (q, k, v), g in zip(layers, shared):
+            sharding.sharded_fst_attention(q, k, v, meta, w.sm_scale, axis, n_units, scatter_to=g, kernel=kernel)
+
     timer = Timer(dev, world)
     g_compute = capture(compute_only)
     for _ in range(3):
@@ -506,6 +520,19 @@ def measure_sharded(fst, name, rank, world, dev, layers_n, reps, kernel="auto"):
             gathers()
         ms_gather = timer(gathers, reps) / reps
         out_bytes = fulls[0].numel() * fulls[0].element_size()
+        if isinstance(shared, list):
+            for _ in range(3):
+                step_fused()
+            ms_fused = timer(step_fused, reps) / reps
+            sent = out_bytes / world * (world - 1)        # what one GPU sends per layer
+            rec["fused"] = {"what": "attention and all-gather in one kernel: each CTA stores its tile into every rank's "
+                                    "copy of the output (TMA stores over NVLink), then a device-side barrier per layer",
+                            "step_ms": ms_fused, "us_per_layer": ms_fused * 1e3 / layers_n,
+                            "nvlink_out_bytes_per_gpu_per_layer": sent,
+                            "nvlink_out_gbs_per_gpu": sent / (ms_fused / layers_n * 1e-3) / 1e9,
+                            "value_gbs": info["gathered_kv_bytes_per_call"] * layers_n / (ms_fused * 1e-3) / 1e9}
+        else:
+            rec["fused"] = {"unavailable": shared}
         rec.update({"step_ms": ms_serial, "step_ms_overlapped": ms_overlap,
                     "all_gather_ms_per_layer": ms_gather / layers_n,
                     "all_gather_bytes_per_layer": out_bytes,
@@ -515,7 +542,13 @@ def measure_sharded(fst, name, rank, world, dev, layers_n, reps, kernel="auto"):
         # ---- parity, outside the timed region: the gathered output of layer 0 against rank 0's
         #      own single-GPU computation of units that another rank (the last one) computed
         step_serial()
+        if isinstance(shared, list):
+            step_fused()
         torch.cuda.synchronize()
+        if isinstance(shared, list):                      # the kernel-gathered tensor against the NCCL-gathered one
+            same = torch.tensor([int(torch.equal(shared[0].local, fulls[0]))], device=dev)
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            rec["fused"]["equals_nccl_gather_on_every_rank"] = bool(same.item())
         if rank == 0:
             units = [n_units - 1, n_units - 2]
             q, k, v = (seeded_full((T, H, N, D), 1000 + j, dev, dtype) for j in range(3))
@@ -546,7 +579,7 @@ def measure_sharded(fst, name, rank, world, dev, layers_n, reps, kernel="auto"):
             rec["parity_vs_oracle_max_abs"] = (fulls[0][sl][:, :, rows].cpu().float() - exact).abs().max().item()
             del q, k, v
     assert fst.last_status(dev) == 0
-    del layers, locals_, fulls, g_compute
+    del layers, locals_, fulls, g_compute, shared
     torch.cuda.empty_cache()
     return rec
 
@@ -627,6 +660,8 @@ def run_ours(args, rank, world):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     w = configs.workload(args.workload)
+    if args.block_m or args.max_ancestors:
+        w = with_block(w, args.block_m or w.block_m, args.max_ancestors or w.max_ancestors)
     info = describe(w)
     dtype = DTYPES[w.dtype]
     T, H, N, D, L = len(w.trees), w.heads, w.n_nodes, w.head_dim, args.layers

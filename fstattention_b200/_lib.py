@@ -24,7 +24,7 @@ EXPORTS = ("fst_version", "fst_status_string", "fst_packed_meta_bytes", "fst_pre
            "fst_attention_fwd_ref", "fst_attention_fwd_ref_static",
            "fst_attention_split_workspace_bytes", "fst_attention_fwd_splitkv", "fst_attention_fwd_gqa", "fst_dfs_order",
            "fst_attention_fwd_paged", "fst_selftest_wait_timeout", "fst_tree_topk_nodes",
-           "fst_build_tree_topk")
+           "fst_build_tree_topk", "fst_attention_fwd_scatter")
 STATIC_SCRATCH_BYTES = 512 * 1024
 
 _lib = None
@@ -47,6 +47,9 @@ def _declare(lib):
     lib.fst_attention_fwd.restype = _i
     lib.fst_attention_fwd.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i]
                                       + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _p])
+    lib.fst_attention_fwd_scatter.restype = _i
+    lib.fst_attention_fwd_scatter.argtypes = ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _sz, _i, _i, _i, _i, _i]
+                                              + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _p])
     lib.fst_attention_split_workspace_bytes.restype = _sz
     lib.fst_attention_split_workspace_bytes.argtypes = [_i, _i, _i, _i, _i]
     lib.fst_attention_fwd_splitkv.restype = _i

@@ -200,6 +200,12 @@ size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, 
     return size_t(kv_splits + 1) * Z * H * n_q * (size_t(head_dim) + 1) * sizeof(float);
 }
 
+// where a call's output goes when it is delivered to every rank of a sharded problem
+struct ScatterTo {
+    void *const *o_ranks;
+    int n_ranks, z0, h0, Z_total, H_total;
+};
+
 static int attention_fwd_impl(const void *q, const void *k, const void *v, void *o, float *lse,
                       const void *packed, size_t meta_tree_stride, int Z, int H, int H_kv, int n_q, int n_kv,
                       int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
@@ -207,7 +213,8 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
                       int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
                       int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
                       int max_ancestors, float sm_scale, int dtype, int kernel, int kv_splits,
-                      void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
+                      void *workspace, size_t workspace_bytes, int32_t *status, void *stream,
+                      const ScatterTo *scatter = nullptr) {
     if (!q || !k || !v || !o || !packed || Z <= 0 || H <= 0 || n_q <= 0 || n_kv < n_q ||
         block_m <= 0 || max_ancestors <= 0)
         return FST_ERR_INVALID_ARG;
@@ -222,7 +229,7 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     kernel &= FST_KERNEL_MASK;
     if (flags & ~FST_KERNEL_FLAG_META_STABLE) return FST_ERR_INVALID_ARG;
 
-    AttnArgs a;
+    AttnArgs a = {};
     a.q = q; a.k = k; a.v = v; a.o = o; a.lse = lse;
     a.packed = static_cast<const unsigned char *>(packed);
     a.meta_stride = meta_tree_stride;
@@ -252,6 +259,26 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     bool rows_aligned = aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o);
     for (int64_t s : strides)
         if ((s * es) & 15) rows_aligned = false;
+
+    if (scatter != nullptr) {
+        // attention + all-gather in one kernel: the TMA tree kernel only, no shared prefix
+        if (scatter->n_ranks < 1 || scatter->n_ranks > kMaxRanks || !scatter->o_ranks) return FST_ERR_INVALID_ARG;
+        if (scatter->z0 < 0 || scatter->h0 < 0 || scatter->z0 + Z > scatter->Z_total || scatter->h0 + H > scatter->H_total)
+            return FST_ERR_INVALID_ARG;
+        if (kernel != FST_KERNEL_AUTO && kernel != FST_KERNEL_TMA && kernel != FST_KERNEL_TMA_T32 && kernel != FST_KERNEL_TMA_T64)
+            return FST_ERR_UNSUPPORTED;
+        if (a.prefix != 0 || !mma_ok(dtype, head_dim, block_m) || block_m < 32) return FST_ERR_UNSUPPORTED;
+        for (int r = 0; r < scatter->n_ranks; ++r) {
+            if (!scatter->o_ranks[r]) return FST_ERR_INVALID_ARG;
+            if (!aligned16(scatter->o_ranks[r])) rows_aligned = false;
+            a.o_ranks[r] = scatter->o_ranks[r];
+        }
+        if (!rows_aligned) return FST_ERR_ALIGNMENT;
+        a.n_out = scatter->n_ranks;
+        a.out_z0 = scatter->z0; a.out_h0 = scatter->h0;
+        a.out_Z = scatter->Z_total; a.out_H = scatter->H_total;
+        return cuda_status(launch_attention_mma(a, dtype, kernel == FST_KERNEL_AUTO ? FST_KERNEL_TMA : kernel, st));
+    }
 
     int choice = kernel;
     const bool automatic = choice == FST_KERNEL_AUTO;
@@ -331,6 +358,24 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
                               stream);
 }
 
+int fst_attention_fwd_scatter(const void *q, const void *k, const void *v, void *const *o_ranks, int n_ranks,
+                              int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
+                              const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
+                              int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                              int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                              int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                              int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n, int block_m,
+                              int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
+                              void *stream) {
+    if (!o_ranks || n_ranks < 1 || n_ranks > kMaxRanks) return FST_ERR_INVALID_ARG;
+    const ScatterTo sc{o_ranks, n_ranks, shard_z0, shard_h0, Z_total, H_total};
+    return attention_fwd_impl(q, k, v, o_ranks[0], lse, packed, meta_tree_stride, Z, H, H, n_q, n_kv, head_dim,
+                              q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
+                              v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,
+                              block_m, max_ancestors, sm_scale, dtype, kernel, 1, nullptr, 0, status,
+                              stream, &sc);
+}
+
 int fst_attention_fwd_splitkv(const void *q, const void *k, const void *v, void *o, float *lse,
                               const void *packed, size_t meta_tree_stride, int Z, int H, int n_q,
                               int n_kv, int head_dim, int64_t q_stride_z, int64_t q_stride_h,
@@ -398,7 +443,7 @@ int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tre
     if (workspace_bytes < fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits))
         return FST_ERR_WORKSPACE;
 
-    AttnArgs a;                                           // the tree part: K/V rows of the tree nodes only
+    AttnArgs a = {};                                      // the tree part: K/V rows of the tree nodes only
     a.q = q; a.k = k_tree; a.v = v_tree; a.o = o; a.lse = lse;
     a.packed = static_cast<const unsigned char *>(packed);
     a.meta_stride = meta_tree_stride;

@@ -105,13 +105,24 @@ struct TmaSmem {
     static constexpr int BYTES = BAR + 64 + 1024;         // + slack to align the base to 1 KB
 };
 
+// Tensor maps of the output: one, or - when the call also delivers its rows to the other GPUs of
+// a sharded problem - one per rank, each over that rank's copy of the full output tensor.
+template <int NOUT>
+struct OutMaps {
+    CUtensorMap m[NOUT];
+};
+
 // PFX = false compiles the shared-prefix machinery (dense tiles, split over CTAs) out: the
 // no-prefix kernel is smaller, and for a latency-bound kernel fewer instruction bytes is time.
-template <typename T, int D, int BM, int TN, bool PFX>
+// NOUT > 1: the attention and the all-gather of its output in one kernel.  Every CTA hands its
+// staged O tile to TMA once per rank, with the coordinates of this rank's shard inside the full
+// tensor (a.out_z0, a.out_h0); stores to the other GPUs' buffers travel over NVLink while other
+// CTAs still compute, so the exchange overlaps the arithmetic tile by tile.
+template <typename T, int D, int BM, int TN, bool PFX, int NOUT>
 __global__ void __launch_bounds__(BM * 2, (BM <= 64 && TN == 32 ? 3 : (BM == 128 && D == 64 && TN == 32 ? 2 : 1)))
 attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                const __grid_constant__ CUtensorMap tm_o) {
+                const __grid_constant__ OutMaps<NOUT> tm_o) {
     using MT = MmaTraits<T>;
     using SM = TmaSmem<D, BM, TN>;
     using TL = SwzTile<D>;
@@ -528,11 +539,15 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     __syncthreads();
     if (tid == 0) {
+        const int n_out = NOUT == 1 ? 1 : a.n_out;
+        const int oh = NOUT == 1 ? h : h + a.out_h0, oz = NOUT == 1 ? z : z + a.out_z0;
+#pragma unroll 1
+        for (int p = 0; p < n_out; ++p)
 #pragma unroll
-        for (int j = 0; j < NB32; ++j)
+            for (int j = 0; j < NB32; ++j)
 #pragma unroll
-            for (int hf = 0; hf < TL::HALVES; ++hf)
-                tma_store_4d(&tm_o, s_base + SM::QO + j * SM::TILE + hf * 4096, hf * 64, row0 + j * 32, h, z);
+                for (int hf = 0; hf < TL::HALVES; ++hf)
+                    tma_store_4d(&tm_o.m[p], s_base + SM::QO + j * SM::TILE + hf * 4096, hf * 64, row0 + j * 32, oh, oz);
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
     }
     if (a.lse != nullptr && t == 0) {
@@ -540,7 +555,10 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         if (ok0) lse[row0 + r0] = m0 * c2 + log2f(l0);
         if (ok1) lse[row0 + r1] = m1 * c2 + log2f(l1);
     }
-    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // smem stays valid until read
+    if (tid == 0) {
+        if (NOUT == 1) asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");   // smem stays valid until read
+        else asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");   // rows bound for other GPUs: until written
+    }
 }
 
 // Merge the partial results of a split prefix: O = sum_s 2^(L_s - L) O_s with L the log-sum-exp of
@@ -713,20 +731,29 @@ inline int sm_count() {
     return n;
 }
 
-template <typename T, int D, int BM, int TN, bool PFX>
+template <typename T, int D, int BM, int TN, bool PFX, int NOUT>
 cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
     using SM = TmaSmem<D, BM, TN>;
     constexpr size_t smem = SM::BYTES;
     constexpr bool bf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
-    alignas(64) CUtensorMap tq, tk, tv, to;
+    alignas(64) CUtensorMap tq, tk, tv;
+    alignas(64) OutMaps<NOUT> to;
     if (!make_map(&tq, a.q, bf16, D, a.n_q, a.H, a.Z, a.qs_n, a.qs_h, a.qs_z) ||
         !make_map(&tk, a.k, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.ks_n, a.ks_h, a.ks_z) ||
-        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z) ||
-        !make_map(&to, a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z))
+        !make_map(&tv, a.v, bf16, D, a.n_kv, a.H / a.kv_group, a.Z, a.vs_n, a.vs_h, a.vs_z))
         return cudaErrorNotSupported;
+    if (NOUT == 1) {
+        if (!make_map(&to.m[0], a.o, bf16, D, a.n_q, a.H, a.Z, a.os_n, a.os_h, a.os_z)) return cudaErrorNotSupported;
+    } else {
+        if (a.n_out < 1 || a.n_out > NOUT) return cudaErrorInvalidValue;
+        for (int p = 0; p < NOUT; ++p)                    // unused entries repeat the last one: never dereferenced
+            if (!make_map(&to.m[p], a.o_ranks[p < a.n_out ? p : a.n_out - 1], bf16, D, a.n_q, a.out_H, a.out_Z,
+                          a.os_n, a.os_h, a.os_z))
+                return cudaErrorNotSupported;
+    }
     static DeviceOnce configured;
     const cudaError_t ce = configured.run([&] {
-        return cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX>,
+        return cudaFuncSetAttribute(attn_tma_kernel<T, D, BM, TN, PFX, NOUT>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     });
     if (ce != cudaSuccess) return ce;
@@ -745,14 +772,18 @@ cudaError_t launch_tma_pfx(const AttnArgs &a, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.skip_prefix ? 0 : 1;                 // beside the prefix kernel an early, waiting grid would hold the SMs it needs
-    return cudaLaunchKernelEx(&cfg, attn_tma_kernel<T, D, BM, TN, PFX>, a, tq, tk, tv, to);
+    return cudaLaunchKernelEx(&cfg, attn_tma_kernel<T, D, BM, TN, PFX, NOUT>, a, tq, tk, tv, to);
 }
 
 template <typename T, int D, int BM, int TN>
 cudaError_t launch_tma_inst(const AttnArgs &a, cudaStream_t stream) {
+    if (a.n_out > 0) {                                    // attention + delivery to every rank; no shared prefix there
+        if (a.prefix > 0 || a.skip_prefix || a.n_splits != 1) return cudaErrorNotSupported;
+        return launch_tma_pfx<T, D, BM, TN, false, kMaxRanks>(a, stream);
+    }
     // the prefix instantiation also writes partial results (skip_prefix), with or without prefix rows
-    return (a.prefix > 0 || a.skip_prefix) ? launch_tma_pfx<T, D, BM, TN, true>(a, stream)
-                                           : launch_tma_pfx<T, D, BM, TN, false>(a, stream);
+    return (a.prefix > 0 || a.skip_prefix) ? launch_tma_pfx<T, D, BM, TN, true, 1>(a, stream)
+                                           : launch_tma_pfx<T, D, BM, TN, false, 1>(a, stream);
 }
 
 // tile_cols: 32, 64, or 0 = by grid size: 64-column tiles up to about eight CTAs per SM (measured:

@@ -118,7 +118,13 @@ struct AttnArgs {
     // the packed metadata was complete before the launch ahead of this one in the stream began:
     // a kernel launched with programmatic stream serialisation may read it before its dependency wait
     int meta_stable;
+    // Delivery of the output to every GPU of a sharded problem (n_out > 0): o_ranks[r] is rank r's
+    // copy of the full output tensor [out_Z][out_H][n_q][D] as mapped into this process, os_*
+    // are that tensor's strides, and this call's (z, h) land at (z + out_z0, h + out_h0).
+    int n_out, out_z0, out_h0, out_Z, out_H;
+    const void *o_ranks[8];
 };
+constexpr int kMaxRanks = 8;
 
 // Prefix rows held in a page pool (a KV cache): pages of page_size rows, pool strides in elements.
 struct PagedArgs {

@@ -142,7 +142,8 @@ def launch_plan(q, prefix, block_m, kernel: str = "auto", kv_splits: Optional[in
 
 def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_scale=None,
                   BLOCK_M=128, MAX_ANCESTORS=64, *, out: Optional[torch.Tensor] = None,
-                  return_lse: bool = False, kernel: str = "auto", kv_splits: Optional[int] = None):
+                  return_lse: bool = False, kernel: str = "auto", kv_splits: Optional[int] = None,
+                  scatter=None):
     """Fused sparse tree attention forward.
 
     ``ancestor_idx, ancestor_mask, leaf_idx`` are the tensors returned by
@@ -156,6 +157,10 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
 
     ``kv_splits`` cuts a shared prefix into that many runs handled by separate CTAs and merged
     afterwards; ``None`` picks a split that fills the GPU when the tree alone does not.
+
+    ``scatter`` (see ``sharding.GatheredOutput.target``) makes the kernel deliver this call's
+    rows into every rank's copy of a full output tensor instead of a local ``out``; the return
+    value is then this rank's copy, complete only after the ranks have met.
 
     Asserts like the reference (fstattention.py:155-157): equal head dims, in {16, 32, 64, 128}.
     """
@@ -172,9 +177,16 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
     n_kv, H_kv = k.shape[2], k.shape[1]
     if k.shape != (Z, H_kv, n_kv, D) or v.shape != k.shape or n_kv < n_q or H_kv < 1 or H % H_kv:
         raise ValueError("k and v must be [Z, H_kv, P + N, D] with P >= 0 and H a multiple of H_kv")
-    o = torch.empty_like(q) if out is None else out
-    if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
-        raise ValueError("out must match q")
+    if scatter is not None:
+        if out is not None:
+            raise ValueError("out= and scatter= exclude each other")
+        o = scatter.local
+        if o.dtype != q.dtype or o.shape[2:] != q.shape[2:] or not o.is_cuda:
+            raise ValueError("the gathered output must have q's dtype, rows and head dimension")
+    else:
+        o = torch.empty_like(q) if out is None else out
+        if o.shape != q.shape or o.dtype != q.dtype or not o.is_cuda:
+            raise ValueError("out must match q")
     lse = torch.empty((Z * H, n_q), device=q.device, dtype=torch.float32) if return_lse else None
 
     lib = _lib.lib()
@@ -239,7 +251,15 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
                 ws.data_ptr() if ws is not None else None, ws_bytes, status.data_ptr(), stream)
         head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                 lse.data_ptr() if lse is not None else None, packed_ptr, packed_stride)
-        if H_kv == H:
+        if scatter is not None:
+            if H_kv != H or n_kv != n_q:
+                raise ValueError("scatter= takes neither grouped-query heads nor a shared prefix")
+            rc = lib.fst_attention_fwd_scatter(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), scatter.pointer_array, scatter.n_ranks,
+                scatter.z0, scatter.h0, o.shape[0], o.shape[1], lse.data_ptr() if lse is not None else None,
+                packed_ptr, packed_stride, *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale),
+                _DTYPES[q.dtype], kern, status.data_ptr(), stream)
+        elif H_kv == H:
             rc = lib.fst_attention_fwd_splitkv(*head, *common_shape, *tail)
         else:                                             # grouped-query attention
             rc = lib.fst_attention_fwd_gqa(*head, Z, H, H_kv, *common_shape[2:], *tail)

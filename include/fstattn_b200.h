@@ -213,6 +213,36 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
                       int32_t *status, void *stream);
 
 /*
+ * fst_attention_fwd on one GPU's shard of a problem split over several GPUs of a node, with the
+ * all-gather of the output done by the attention kernel itself.  (No counterpart in the
+ * reference, which is single-GPU; its programs are independent, fstattention.py:42-45, grid
+ * :159, so a batch of trees splits by tree and a single tree by head.)
+ *
+ * Every rank holds the full output tensor [Z_total][H_total][n_q][head_dim] (strides
+ * o_stride_*, the same on all ranks) and has the other ranks' copies mapped into its address
+ * space (CUDA IPC or virtual-memory export; peer access enabled): o_ranks[r] is rank r's copy as
+ * THIS process addresses it, this rank's own included, n_ranks <= 8, a HOST array.  q, k, v are
+ * this rank's shard, [Z][H][..][head_dim]; its (z, h) is element (shard_z0 + z, shard_h0 + h) of
+ * the full tensor.  Each CTA stores its finished tile once per rank (TMA stores, no multicast),
+ * so rows cross NVLink while other CTAs still compute.  When the kernel has finished on the
+ * stream this rank's rows are in place everywhere; before anyone reads a full tensor, and before
+ * a buffer is written again, the ranks must meet (a barrier on the streams: the caller's job).
+ * Tensor-core TMA kernel only: fp16 / bf16, head_dim 64 or 128, block_m 32, 64 or 128, no shared
+ * prefix (n_kv == n_q), kernel = FST_KERNEL_AUTO or one of FST_KERNEL_TMA*; FST_ERR_UNSUPPORTED
+ * otherwise.  lse, when given, is this shard's [Z][H][n_q] and stays local.
+ */
+int fst_attention_fwd_scatter(const void *q, const void *k, const void *v, void *const *o_ranks, int n_ranks,
+                              int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
+                              const void *packed, size_t meta_tree_stride,
+                              int Z, int H, int n_q, int n_kv, int head_dim,
+                              int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
+                              int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
+                              int64_t v_stride_z, int64_t v_stride_h, int64_t v_stride_n,
+                              int64_t o_stride_z, int64_t o_stride_h, int64_t o_stride_n,
+                              int block_m, int max_ancestors, float sm_scale, int dtype, int kernel,
+                              int32_t *status, void *stream);
+
+/*
  * fst_attention_fwd with the shared prefix cut into kv_splits runs of rows, each handled by its
  * own CTA per (block, head, batch) - the decode case, where a long prompt meets a tree too small
  * to fill the GPU (the reference walks the prefix in one program, fstattention.py:113-136).

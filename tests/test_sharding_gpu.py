@@ -38,6 +38,16 @@ def _worker(rank, world, port, result_dir):
             meta_all = fst.build_tree_metadata(trees if T > 1 else trees[0], 64, 128)
             single = fst.fst_attention(q.to(dev), k.to(dev), v.to(dev), meta_all, sm_scale=D ** -0.5)
             assert torch.equal(got, single), (axis, rank)
+            # the same with the gather done by the attention kernel: every CTA stores its tile
+            # into both ranks' copies of the full tensor, then the ranks meet on the stream
+            shared = sharding.GatheredOutput((T, H, N, D), torch.float16, dev)
+            shared.local.fill_(float("nan"))
+            shared.meet()
+            fused = sharding.sharded_fst_attention(ql, kl, vl, meta, D ** -0.5, axis, total, scatter_to=shared)
+            torch.cuda.synchronize()
+            assert fused.data_ptr() == shared.local.data_ptr()
+            assert torch.equal(fused, single), (axis, rank, "fused")
+            shared.meet()
             if rank == 0:
                 t = T - 1
                 lin, _ = orc.lineage_from_parent(trees[t])
