@@ -1,6 +1,7 @@
 // A caller of the C ABI with no Python and no torch: builds the block metadata of a small tree,
 // runs tree attention in fp32, and checks the result against a plain loop on the host.
 // Build: nvcc -I include tests/cabi/cabi_example.cu -L fstattention_b200 -lfstattn_b200 -o cabi_example
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -83,5 +84,50 @@ int main() {
             }
         }
     std::printf("fst_version %d, max-abs difference from the host loop %.3e\n", fst_version(), worst);
-    return worst <= 2e-5 ? 0 : 1;
+    if (worst > 2e-5) return 1;
+
+    // Host cost of the entry point at a decoder's shapes (fp16, 32 heads x 256 nodes x 128, 64-row
+    // blocks): how long fst_attention_fwd takes to return, on sixteen rotating layer buffers, with
+    // the flag that lets the kernel fetch its index lists early.  After the first round the
+    // library encodes no tensor map any more (they are kept per thread), so a call is argument
+    // checks plus one launch.
+    {
+        const int N2 = 256, H2 = 32, D2 = 128, BM2 = 64, MA2 = 256, LAYERS = 16, NB2 = N2 / BM2;
+        std::vector<int32_t> par2(N2);
+        par2[0] = -1;
+        for (int i = 1; i < N2; ++i) par2[i] = (i * 7 + 3) % i;
+        int32_t *d_par2;
+        void *d_packed2, *d_buf;
+        const size_t pk2 = fst_packed_meta_bytes(NB2, BM2, MA2), tensor = size_t(H2) * N2 * D2 * 2;
+        CHECK_CUDA(cudaMalloc(&d_par2, N2 * sizeof(int32_t)));
+        CHECK_CUDA(cudaMalloc(&d_packed2, pk2));
+        CHECK_CUDA(cudaMalloc(&d_buf, tensor * 4 * LAYERS));
+        CHECK_CUDA(cudaMemset(d_buf, 0, tensor * 4 * LAYERS));
+        CHECK_CUDA(cudaMemcpy(d_par2, par2.data(), N2 * sizeof(int32_t), cudaMemcpyHostToDevice));
+        CHECK_FST(fst_precompute(d_par2, 1, N2, BM2, MA2, nullptr, nullptr, nullptr, d_packed2, pk2, d_status, stream));
+        auto layer_call = [&](int l, int flags) {
+            char *base = static_cast<char *>(d_buf) + size_t(l) * 4 * tensor;
+            return fst_attention_fwd(base, base + tensor, base + 2 * tensor, base + 3 * tensor, nullptr, d_packed2, 0, 1, H2,
+                                     N2, N2, D2, int64_t(H2) * N2 * D2, int64_t(N2) * D2, D2, int64_t(H2) * N2 * D2,
+                                     int64_t(N2) * D2, D2, int64_t(H2) * N2 * D2, int64_t(N2) * D2, D2,
+                                     int64_t(H2) * N2 * D2, int64_t(N2) * D2, D2, BM2, MA2, 0.088f, FST_F16,
+                                     FST_KERNEL_AUTO | flags, d_status, stream);
+        };
+        for (int l = 0; l < LAYERS; ++l) CHECK_FST(layer_call(l, l ? FST_KERNEL_FLAG_META_STABLE : 0));
+        CHECK_CUDA(cudaStreamSynchronize(stream));
+        const int rounds = 200;
+        const auto t0 = std::chrono::steady_clock::now();
+        for (int r = 0; r < rounds; ++r)
+            for (int l = 0; l < LAYERS; ++l) CHECK_FST(layer_call(l, FST_KERNEL_FLAG_META_STABLE));
+        const auto t1 = std::chrono::steady_clock::now();
+        CHECK_CUDA(cudaStreamSynchronize(stream));
+        const auto t2 = std::chrono::steady_clock::now();
+        const double calls = double(rounds) * LAYERS;
+        std::printf("host time per fst_attention_fwd call: %.2f us to return, %.2f us per call until the stream is idle\n",
+                    std::chrono::duration<double, std::micro>(t1 - t0).count() / calls,
+                    std::chrono::duration<double, std::micro>(t2 - t0).count() / calls);
+        CHECK_CUDA(cudaMemcpy(status, d_status, sizeof(status), cudaMemcpyDeviceToHost));
+        if (status[0] != 0) { std::printf("device status %d (%s)\n", status[0], fst_status_string(status[0])); return 4; }
+    }
+    return 0;
 }

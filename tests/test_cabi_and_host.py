@@ -200,3 +200,5 @@ def test_c_program_against_the_library(built_lib, tmp_path):
     run = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "max-abs difference" in run.stdout
+    assert "host time per fst_attention_fwd call" in run.stdout
+    print(run.stdout)
