@@ -15,7 +15,7 @@ STATUS_WORDS = 4
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 KERNEL_FLAG_META_STABLE = 0x100
 KERNELS = {"auto": 0, "simt": 1, "mma": 2, "tma": 3, "tma_t32": 4, "tma_t64": 5,
-           "tma_umma": 6, "persist": 7, "lean": 8}
+           "tma_umma": 6, "persist": 7}
 DEV_MALFORMED_TREE, DEV_ANCESTOR_OVERFLOW, DEV_INDEX_RANGE = 16, 17, 18
 
 # every symbol include/fstattn_b200.h declares

@@ -285,14 +285,14 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
     if (automatic)
         choice = (mma_ok(dtype, head_dim, block_m) && rows_aligned) ? FST_KERNEL_TMA : FST_KERNEL_SIMT;
     if (choice == FST_KERNEL_SIMT) return cuda_status(launch_attention_simt(a, dtype, st));
-    if (choice < FST_KERNEL_MMA || choice > FST_KERNEL_LEAN) return FST_ERR_INVALID_ARG;
+    if (choice < FST_KERNEL_MMA || choice > FST_KERNEL_PERSIST) return FST_ERR_INVALID_ARG;
     if (!mma_ok(dtype, head_dim, block_m)) return FST_ERR_UNSUPPORTED;
     if (!rows_aligned) return FST_ERR_ALIGNMENT;
 
     // A shared prefix with a workspace: either the tcgen05 prefix kernel takes it in kv_splits runs
     // while the tree kernel does the tree part (head_dim 64 or 128; chosen automatically from 256
     // prefix rows on), or the tree kernel itself is launched kv_splits times over the prefix.
-    const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA && choice != FST_KERNEL_PERSIST && choice != FST_KERNEL_LEAN;
+    const bool can_part = a.prefix > 0 && workspace != nullptr && choice != FST_KERNEL_MMA && choice != FST_KERNEL_PERSIST;
     // (the tcgen05 kernel takes Q from shared memory as it arrived, so it cannot flip Q's sign
     // for a negative factor; the tree kernel walks the prefix itself then)
     const bool want_umma = can_part && (head_dim == 128 || head_dim == 64) && sm_scale > 0.f &&

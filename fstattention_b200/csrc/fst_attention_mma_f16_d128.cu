@@ -1,11 +1,9 @@
 // Instantiates the tensor-core tree-attention kernels for f16, head_dim 128.
-#include "fst_attention_lean.cuh"
 #include "fst_attention_persist.cuh"
 
 namespace fst {
 cudaError_t launch_mma_f16_d128(const AttnArgs &a, int variant, cudaStream_t stream) {
     if (variant == FST_KERNEL_PERSIST) return launch_persist_d<__half, 128>(a, stream);
-    if (variant == FST_KERNEL_LEAN) return launch_lean_d<__half, 128>(a, stream);
     if (variant == FST_KERNEL_TMA) {
         if (persist_pays(a)) {                             // many items per SM: the persistent kernel
             const cudaError_t e = launch_persist_d<__half, 128>(a, stream);

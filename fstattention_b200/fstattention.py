@@ -131,8 +131,8 @@ def launch_plan(q, prefix, block_m, kernel: str = "auto", kv_splits: Optional[in
         and block_m in (16, 32, 64, 128)
     tree = "attn_simt_kernel" if kernel == "simt" or not tensor_core else \
         "attn_mma_kernel" if kernel == "mma" or block_m == 16 else "attn_tma_kernel"
-    if kernel in ("persist", "lean") and tree == "attn_tma_kernel" and prefix == 0 and block_m in (64, 128):
-        tree = f"attn_{kernel}_kernel"
+    if kernel == "persist" and tree == "attn_tma_kernel" and prefix == 0 and block_m in (64, 128):
+        tree = "attn_persist_kernel"                      # by hand only: it measured slower than attn_tma_kernel
     if need_ws and q.shape[-1] in (64, 128) and (kernel == "tma_umma" or (kernel == "auto" and prefix >= 256)):
         return {"kernels": ["prefix_umma_kernel", tree, "combine_splits_kernel"], "prefix_runs": splits}
     if need_ws:

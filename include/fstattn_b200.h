@@ -61,14 +61,10 @@ enum fst_kernel {
     FST_KERNEL_TMA_T64 = 5,        /* ... forced 64-column tiles (fewest softmax rounds)         */
     FST_KERNEL_TMA_UMMA = 6,       /* tree part as FST_KERNEL_TMA, shared prefix by the tcgen05  */
                                    /* kernel (head_dim 64 / 128, fst_attention_fwd_splitkv only) */
-    FST_KERNEL_PERSIST = 7,        /* persistent CTAs, a producer warp streaming tiles through a */
+    FST_KERNEL_PERSIST = 7         /* persistent CTAs, a producer warp streaming tiles through a */
                                    /* shared-memory ring ahead of the arithmetic: block_m 64 or  */
                                    /* 128, no prefix.  Slower than FST_KERNEL_TMA on every shape */
                                    /* measured, so never the automatic choice                    */
-    FST_KERNEL_LEAN = 8            /* the TMA kernel cut down to 128 registers and 48 KB so that  */
-                                   /* four CTAs (sixteen warps) share an SM: Q fragments re-read  */
-                                   /* from shared memory, the block's own rows streamed through   */
-                                   /* two stages like the gathered ones; block_m 64 / 128, no prefix */
 };
 
 /*

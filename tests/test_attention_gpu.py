@@ -31,8 +31,8 @@ def kernels_for(dtype, d, bm, prefix=0):
     ks = ["auto", "simt"]
     if dtype in (torch.float16, torch.bfloat16) and d in (64, 128) and bm in (16, 32, 64, 128):
         ks += ["mma"] + (["tma_t32", "tma_t64"] if bm >= 32 else [])
-        if bm in (64, 128) and prefix == 0:              # the persistent and the four-CTA kernels: no shared prefix
-            ks += ["persist", "lean"]
+        if bm in (64, 128) and prefix == 0:              # the persistent kernel: no shared prefix
+            ks.append("persist")
     return ks
 
 
@@ -138,7 +138,7 @@ def test_full_size_equal_scores_property(fst, name):
     q = torch.randn((T, H, n, D), generator=g).half()
     k = torch.zeros_like(v)
     meta = fst.build_tree_metadata(w.trees if T > 1 else w.trees[0], w.block_m, w.max_ancestors)
-    for kern in ("mma", "tma_t32", "tma_t64", "persist", "lean"):
+    for kern in ("mma", "tma_t32", "tma_t64", "persist"):
         o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
         for t in range(0, T, 9):
             want = chain_mean_values(w.trees[t], v[t].double().numpy())
@@ -158,7 +158,7 @@ def test_full_size_kernels_agree(fst):
     q, k, v = (x.cuda() for x in make_qkv(1, w.heads, w.n_nodes, w.n_nodes, w.head_dim, torch.float16, 17))
     meta = fst.build_tree_metadata(w.trees[0], w.block_m, w.max_ancestors)
     base = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel="simt")
-    for kern in ("mma", "tma_t32", "tma_t64", "persist", "lean"):
+    for kern in ("mma", "tma_t32", "tma_t64", "persist"):
         o = fst.fst_attention(q, k, v, meta, sm_scale=w.sm_scale, kernel=kern)
         assert maxabs(o, base) <= TOL_F16, kern
 
@@ -673,7 +673,7 @@ def test_forest64_full_size_against_the_oracle(fst):
     q, k, v = make_qkv(T, H, n, n, D, torch.float16, seed=61)
     meta = fst.build_tree_metadata(w.trees, w.block_m, w.max_ancestors, reference_format=False)
     outs = {kern: fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
-            for kern in ("auto", "tma_t32", "persist", "lean")}
+            for kern in ("auto", "tma_t32", "persist")}
     worst = dict.fromkeys(outs, 0.0)
     for t in range(T):
         exact = oracle_attention(q[t:t + 1], k[t:t + 1], v[t:t + 1], w.trees[t], w.sm_scale,
@@ -696,7 +696,7 @@ def test_deep4096_all_heads_row_slices_against_the_oracle(fst):
     mask = orc.full_attention_mask(lin, pad_rows=0)
     rows = torch.cat([torch.arange(0, 64), torch.arange(2048, 2112), torch.arange(n - 128, n)])
     exact = orc.dense_tree_attention(q[:, :, rows], k, v, mask[rows], w.sm_scale, torch.float32, head_chunk=8)
-    for kern in ("auto", "persist", "lean"):
+    for kern in ("auto", "persist"):
         o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
         assert maxabs(o[:, :, rows], exact) <= TOL_F16, kern
     assert fst.last_status() == 0
