@@ -48,7 +48,7 @@ def _declare(lib):
     lib.fst_attention_fwd.argtypes = ([_p, _p, _p, _p, _p, _p, _sz, _i, _i, _i, _i, _i]
                                       + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _p])
     lib.fst_attention_fwd_scatter.restype = _i
-    lib.fst_attention_fwd_scatter.argtypes = ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p, _sz, _i, _i, _i, _i, _i]
+    lib.fst_attention_fwd_scatter.argtypes = ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _sz, _i, _i, _i, _i, _i]
                                               + _TENSOR_STRIDES + [_i, _i, _f, _i, _i, _p, _p])
     lib.fst_attention_split_workspace_bytes.restype = _sz
     lib.fst_attention_split_workspace_bytes.argtypes = [_i, _i, _i, _i, _i]

@@ -203,7 +203,7 @@ size_t fst_attention_split_workspace_bytes(int Z, int H, int n_q, int head_dim, 
 // where a call's output goes when it is delivered to every rank of a sharded problem
 struct ScatterTo {
     void *const *o_ranks;
-    int n_ranks, z0, h0, Z_total, H_total;
+    int n_ranks, rank, z0, h0, Z_total, H_total;
 };
 
 static int attention_fwd_impl(const void *q, const void *k, const void *v, void *o, float *lse,
@@ -262,7 +262,9 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
 
     if (scatter != nullptr) {
         // attention + all-gather in one kernel: the TMA tree kernel only, no shared prefix
-        if (scatter->n_ranks < 1 || scatter->n_ranks > kMaxRanks || !scatter->o_ranks) return FST_ERR_INVALID_ARG;
+        if (scatter->n_ranks < 1 || scatter->n_ranks > kMaxRanks || !scatter->o_ranks || scatter->rank < 0 ||
+            scatter->rank >= scatter->n_ranks)
+            return FST_ERR_INVALID_ARG;
         if (scatter->z0 < 0 || scatter->h0 < 0 || scatter->z0 + Z > scatter->Z_total || scatter->h0 + H > scatter->H_total)
             return FST_ERR_INVALID_ARG;
         if (kernel != FST_KERNEL_AUTO && kernel != FST_KERNEL_TMA && kernel != FST_KERNEL_TMA_T32 && kernel != FST_KERNEL_TMA_T64)
@@ -275,6 +277,7 @@ static int attention_fwd_impl(const void *q, const void *k, const void *v, void 
         }
         if (!rows_aligned) return FST_ERR_ALIGNMENT;
         a.n_out = scatter->n_ranks;
+        a.out_rank = scatter->rank;
         a.out_z0 = scatter->z0; a.out_h0 = scatter->h0;
         a.out_Z = scatter->Z_total; a.out_H = scatter->H_total;
         return cuda_status(launch_attention_mma(a, dtype, kernel == FST_KERNEL_AUTO ? FST_KERNEL_TMA : kernel, st));
@@ -359,7 +362,7 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
 }
 
 int fst_attention_fwd_scatter(const void *q, const void *k, const void *v, void *const *o_ranks, int n_ranks,
-                              int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
+                              int my_rank, int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
                               const void *packed, size_t meta_tree_stride, int Z, int H, int n_q, int n_kv,
                               int head_dim, int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
                               int64_t k_stride_z, int64_t k_stride_h, int64_t k_stride_n,
@@ -368,7 +371,7 @@ int fst_attention_fwd_scatter(const void *q, const void *k, const void *v, void 
                               int max_ancestors, float sm_scale, int dtype, int kernel, int32_t *status,
                               void *stream) {
     if (!o_ranks || n_ranks < 1 || n_ranks > kMaxRanks) return FST_ERR_INVALID_ARG;
-    const ScatterTo sc{o_ranks, n_ranks, shard_z0, shard_h0, Z_total, H_total};
+    const ScatterTo sc{o_ranks, n_ranks, my_rank, shard_z0, shard_h0, Z_total, H_total};
     return attention_fwd_impl(q, k, v, o_ranks[0], lse, packed, meta_tree_stride, Z, H, H, n_q, n_kv, head_dim,
                               q_stride_z, q_stride_h, q_stride_n, k_stride_z, k_stride_h, k_stride_n,
                               v_stride_z, v_stride_h, v_stride_n, o_stride_z, o_stride_h, o_stride_n,

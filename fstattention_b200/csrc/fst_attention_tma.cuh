@@ -541,13 +541,19 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     if (tid == 0) {
         const int n_out = NOUT == 1 ? 1 : a.n_out;
         const int oh = NOUT == 1 ? h : h + a.out_h0, oz = NOUT == 1 ? z : z + a.out_z0;
+        // Every rank starts with its own copy and then walks the others in ring order from its
+        // right-hand neighbour on: at any moment the ranks' stores then head for different GPUs
+        // (all starting at rank 0 would have seven senders share one receiver's links).
+        int p = NOUT == 1 ? 0 : a.out_rank;
 #pragma unroll 1
-        for (int p = 0; p < n_out; ++p)
+        for (int i = 0; i < n_out; ++i) {
 #pragma unroll
             for (int j = 0; j < NB32; ++j)
 #pragma unroll
                 for (int hf = 0; hf < TL::HALVES; ++hf)
                     tma_store_4d(&tm_o.m[p], s_base + SM::QO + j * SM::TILE + hf * 4096, hf * 64, row0 + j * 32, oh, oz);
+            p = p + 1 == n_out ? 0 : p + 1;
+        }
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
     }
     if (a.lse != nullptr && t == 0) {

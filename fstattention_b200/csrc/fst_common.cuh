@@ -121,7 +121,7 @@ struct AttnArgs {
     // Delivery of the output to every GPU of a sharded problem (n_out > 0): o_ranks[r] is rank r's
     // copy of the full output tensor [out_Z][out_H][n_q][D] as mapped into this process, os_*
     // are that tensor's strides, and this call's (z, h) land at (z + out_z0, h + out_h0).
-    int n_out, out_z0, out_h0, out_Z, out_H;
+    int n_out, out_rank, out_z0, out_h0, out_Z, out_H;      // out_rank: which of o_ranks is this GPU's own
     const void *o_ranks[8];
 };
 constexpr int kMaxRanks = 8;

@@ -255,7 +255,7 @@ def fst_attention(q, k, v, ancestor_idx, ancestor_mask=None, leaf_idx=None, sm_s
             if H_kv != H or n_kv != n_q:
                 raise ValueError("scatter= takes neither grouped-query heads nor a shared prefix")
             rc = lib.fst_attention_fwd_scatter(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), scatter.pointer_array, scatter.n_ranks,
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), scatter.pointer_array, scatter.n_ranks, scatter.rank,
                 scatter.z0, scatter.h0, o.shape[0], o.shape[1], lse.data_ptr() if lse is not None else None,
                 packed_ptr, packed_stride, *common_shape, BLOCK_M, MAX_ANCESTORS, float(sm_scale),
                 _DTYPES[q.dtype], kern, status.data_ptr(), stream)

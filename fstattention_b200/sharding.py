@@ -57,7 +57,8 @@ class GatheredOutput:
         if self.n_ranks > 8:
             raise ValueError("at most 8 ranks")
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        if ptrs[dist.get_rank(group)] != self.local.data_ptr():
+        self.rank = dist.get_rank(group)
+        if ptrs[self.rank] != self.local.data_ptr():
             raise RuntimeError("symmetric memory handle does not describe the local buffer")
         self.pointer_array = (ctypes.c_void_p * self.n_ranks)(*ptrs)
         self.z0 = self.h0 = 0

@@ -221,7 +221,8 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * Every rank holds the full output tensor [Z_total][H_total][n_q][head_dim] (strides
  * o_stride_*, the same on all ranks) and has the other ranks' copies mapped into its address
  * space (CUDA IPC or virtual-memory export; peer access enabled): o_ranks[r] is rank r's copy as
- * THIS process addresses it, this rank's own included, n_ranks <= 8, a HOST array.  q, k, v are
+ * THIS process addresses it, this rank's own (o_ranks[my_rank]) included, n_ranks <= 8, a HOST
+ * array.  q, k, v are
  * this rank's shard, [Z][H][..][head_dim]; its (z, h) is element (shard_z0 + z, shard_h0 + h) of
  * the full tensor.  Each CTA stores its finished tile once per rank (TMA stores, no multicast),
  * so rows cross NVLink while other CTAs still compute.  When the kernel has finished on the
@@ -232,7 +233,7 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * otherwise.  lse, when given, is this shard's [Z][H][n_q] and stays local.
  */
 int fst_attention_fwd_scatter(const void *q, const void *k, const void *v, void *const *o_ranks, int n_ranks,
-                              int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
+                              int my_rank, int shard_z0, int shard_h0, int Z_total, int H_total, float *lse,
                               const void *packed, size_t meta_tree_stride,
                               int Z, int H, int n_q, int n_kv, int head_dim,
                               int64_t q_stride_z, int64_t q_stride_h, int64_t q_stride_n,
