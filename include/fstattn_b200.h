@@ -224,7 +224,7 @@ int fst_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * THIS process addresses it, this rank's own (o_ranks[my_rank]) included, n_ranks <= 8, a HOST
  * array.  q, k, v are
  * this rank's shard, [Z][H][..][head_dim]; its (z, h) is element (shard_z0 + z, shard_h0 + h) of
- * the full tensor.  Each CTA stores its finished tile once per rank (TMA stores, no multicast),
+ * the full tensor.  Each CTA stores its finished tile once per rank (plain TMA stores, one per rank),
  * so rows cross NVLink while other CTAs still compute.  When the kernel has finished on the
  * stream this rank's rows are in place everywhere; before anyone reads a full tensor, and before
  * a buffer is written again, the ranks must meet (a barrier on the streams: the caller's job).
