@@ -339,6 +339,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         gathered_words(0, w0n, w1n);
     }
     bool v_here = false;                                  // the block's V rows have been waited for
+    bool have_acc = false;                                // some product has been added to acc
 #pragma unroll 1
     for (int i = 0; i < n_tiles; ++i) {
         const bool blk = i < nblk;
@@ -453,7 +454,8 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             }
             l0 = l0 * al0 + ps0;
             l1 = l1 * al1 + ps1;
-            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+            // (nothing to rescale before the first product: the accumulators are still zero)
+            if (have_acc && __any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
 #pragma unroll
                 for (int d = 0; d < ND; ++d) {
                     acc[d][0] *= al0; acc[d][1] *= al0;
@@ -468,6 +470,7 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         }
 
         if (any) {
+            have_acc = true;
             // ---- O += P V
             const int vrow = (((lane >> 3) & 1) << 3) + (lane & 7), vch = lane >> 4;
 #pragma unroll
@@ -526,14 +529,19 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     }
     if (nt_gat > 1) __syncthreads();                      // stage 1 shares this memory
     {
-        const uint32_t ob0 = s_base + SM::QO + (r0 >> 5) * SM::TILE + t * 4;
-        const uint32_t ob1 = s_base + SM::QO + (r1 >> 5) * SM::TILE + t * 4;
+        // stmatrix.x4 stores four 8x8 tiles in the accumulators' own fragment layout: rows g and
+        // g + 8 of two neighbouring 8-column blocks per instruction.  Lane l gives the address of
+        // row (l & 7) + 8 * ((l >> 3) & 1) of my warp's sixteen rows in column block d + (l >> 4).
+        const int sr = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const uint32_t ob = s_base + SM::QO + (sr >> 5) * SM::TILE;
 #pragma unroll
-        for (int d = 0; d < ND; ++d) {
+        for (int d = 0; d < ND; d += 2) {
             const uint32_t v0 = MT::pack(acc[d][0] * inv0, acc[d][1] * inv0);
             const uint32_t v1 = MT::pack(acc[d][2] * inv1, acc[d][3] * inv1);
-            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ob0 + TL::off(r0 & 31, d)), "r"(v0) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ob1 + TL::off(r1 & 31, d)), "r"(v1) : "memory");
+            const uint32_t v2 = MT::pack(acc[d + 1][0] * inv0, acc[d + 1][1] * inv0);
+            const uint32_t v3 = MT::pack(acc[d + 1][2] * inv1, acc[d + 1][3] * inv1);
+            asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};\n"
+                         ::"r"(ob + TL::off(sr & 31, d + (lane >> 4))), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
         }
     }
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
