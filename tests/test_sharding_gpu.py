@@ -20,7 +20,8 @@ def _worker(rank, world, port, result_dir):
     dist.init_process_group("nccl", rank=rank, world_size=world)
     try:
         dev = torch.device("cuda", rank)
-        for axis, trees, H in (("tree", configs.jittered_forest(3, 6, 256), 4), ("head", [configs.deep_chain_tree(0, 1024)], 8)):
+        for axis, trees, H in (("tree", configs.jittered_forest(3, 6, 256), 4), ("head", [configs.deep_chain_tree(0, 1024)], 8),
+                               ("tree", configs.jittered_forest(4, 5, 256), 2)):      # five trees: shards of three and two
             T, N, D = len(trees), len(trees[0]), 128
             g = torch.Generator().manual_seed(5)
             q, k, v = (torch.randn((T, H, N, D), generator=g).half() for _ in range(3))
@@ -30,9 +31,12 @@ def _worker(rank, world, port, result_dir):
             mine = trees[lo:hi] if axis == "tree" else trees
             meta = fst.build_tree_metadata(mine if len(mine) > 1 else mine[0], 64, 128)
             full = torch.empty((T, H, N, D), dtype=torch.float16, device=dev)
-            got, work = sharding.sharded_fst_attention(ql, kl, vl, meta, D ** -0.5, axis, total, gathered=full,
-                                                       async_gather=True)
-            work.wait()
+            if total % world == 0:
+                got, work = sharding.sharded_fst_attention(ql, kl, vl, meta, D ** -0.5, axis, total, gathered=full,
+                                                           async_gather=True)
+                work.wait()
+            else:                                        # unequal shards: NCCL gathers padded shards and trims
+                got = sharding.sharded_fst_attention(ql, kl, vl, meta, D ** -0.5, axis, total, gathered=full)
             torch.cuda.synchronize()
             # one GPU, whole problem
             meta_all = fst.build_tree_metadata(trees if T > 1 else trees[0], 64, 128)
