@@ -56,6 +56,15 @@ def test_host_only_entry_points(built_lib):
     assert lib.fst_packed_meta_bytes(4, 64, 64) == 16 + 4 * 64 * 4 + 4 * 64 * 2 * 4 + 4 * 64 * 2 * 4
     assert lib.fst_packed_meta_bytes(0, 64, 64) == 0
     assert lib.fst_attention_ref_workspace_bytes(2, 256, 64, 64) == 2 * lib.fst_packed_meta_bytes(4, 64, 64)
+    # the device-built forest has the reference's node counts (utils.py:27-40: 2^(depth+3) - 4)
+    for depth in (5, 7, 9):
+        assert lib.fst_tree_topk_nodes(depth, 4, 0.5) == 2 ** (depth + 3) - 4
+    assert lib.fst_tree_topk_nodes(14, 4, 0.5) == -1          # a level of 32768 nodes: beyond the kernel
+    assert lib.fst_tree_topk_nodes(7, 4, 1.5) == -1
+    assert lib.fst_build_tree_topk(None, 1, 7, 4, 0.5, 1020, None, None, None, None) == 1
+    assert lib.fst_build_tree_topk(ctypes.c_void_p(256), 1, 14, 4, 0.5, 1 << 20, ctypes.c_void_p(256), None, None, None) == 6
+    assert lib.fst_attention_fwd_scatter(None, None, None, None, 2, 0, 0, 0, 2, 2, None, None, 0, 1, 1, 4, 4, 64,
+                                         *([1] * 12), 64, 64, 1.0, 0, 0, None, None) == 1
     # argument checks happen before any CUDA call
     assert lib.fst_precompute(None, 1, 4, 16, 16, None, None, None, None, 0, None, None) == 1
     assert lib.fst_precompute(ctypes.c_void_p(256), 1, 1 << 20, 16, 16, None, None, None, None, 0, None, None) == 6
