@@ -300,7 +300,8 @@ int fst_attention_fwd_gqa(const void *q, const void *k, const void *v, void *o, 
  * the tree kernel, partial results through `workspace`
  * (fst_attention_split_workspace_bytes(Z, H, n_q, head_dim, kv_splits) bytes).  A page number
  * outside [0, n_pages) reads as zeros and sets FST_DEV_INDEX_RANGE.  block_table and prefix_lens
- * are device pointers.
+ * are device pointers.  sm_scale must be positive here (the tcgen05 prefix kernel takes Q as it
+ * lies in shared memory and cannot fold a sign into it): FST_ERR_INVALID_ARG otherwise.
  */
 int fst_attention_fwd_paged(const void *q, const void *k_tree, const void *v_tree, void *o, float *lse,
                             const void *packed, size_t meta_tree_stride,
