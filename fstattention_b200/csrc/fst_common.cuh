@@ -118,6 +118,8 @@ struct AttnArgs {
     // the packed metadata was complete before the launch ahead of this one in the stream began:
     // a kernel launched with programmatic stream serialisation may read it before its dependency wait
     int meta_stable;
+    // grid order of the TMA tree kernel: heads fastest and blocks from the last one down (grids of a few waves)
+    int heads_first;
     // Delivery of the output to every GPU of a sharded problem (n_out > 0): o_ranks[r] is rank r's
     // copy of the full output tensor [out_Z][out_H][n_q][D] as mapped into this process, os_*
     // are that tensor's strides, and this call's (z, h) land at (z + out_z0, h + out_h0).
