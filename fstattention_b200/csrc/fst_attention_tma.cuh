@@ -209,6 +209,18 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
         wb0[p] = (tree && ok0) ? __ldg(g_bmask + r0 * BW + p) : 0u;
         wb1[p] = (tree && ok1) ? __ldg(g_bmask + r1 * BW + p) : 0u;
     }
+    // With at most 64 ancestor slots (two mask words per row: the reference's MAX_ANCESTORS) the
+    // 32-column-tile instantiations fetch the words of the gathered tiles here too, with everything
+    // else, instead of one tile ahead inside the loop, where a loaded L2 answers later than a tile
+    // takes (2 % on 64 batched trees; the 64-column instantiations lose by the extra choice).
+    constexpr int PRE = TN == 32 ? 2 : 0;
+    const bool pre = PRE > 0 && maw <= PRE;
+    uint32_t pe0[PRE + 1], pe1[PRE + 1];
+#pragma unroll
+    for (int p = 0; p < PRE; ++p) {
+        pe0[p] = (pre && tree && ok0 && p < maw) ? __ldg(g_emask + r0 * maw + p) : 0u;
+        pe1[p] = (pre && tree && ok1 && p < maw) ? __ldg(g_emask + r1 * maw + p) : 0u;
+    }
     if (tid == 0) {                                       // shared memory only: needs no wait either
         mbar_init(bar_qk, 1);
         mbar_init(bar_v, 1);
@@ -322,8 +334,14 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
             w0[p] = w1[p] = 0u;
             if (e < nt_ext) {
                 const int wi = e * TP + p;
-                if (ok0 && wi < maw) w0[p] = __ldg(g_emask + r0 * maw + wi);
-                if (ok1 && wi < maw) w1[p] = __ldg(g_emask + r1 * maw + wi);
+                if (pre) {
+#pragma unroll
+                    for (int q = 0; q < PRE; ++q)
+                        if (q == wi) { w0[p] = pe0[q]; w1[p] = pe1[q]; }
+                } else {
+                    if (ok0 && wi < maw) w0[p] = __ldg(g_emask + r0 * maw + wi);
+                    if (ok1 && wi < maw) w1[p] = __ldg(g_emask + r1 * maw + wi);
+                }
             } else if (e < nt_gat) {
                 const int rem = p_end - p_lo - (e - nt_ext) * TN - p * 32;
                 w0[p] = w1[p] = rem >= 32 ? 0xffffffffu : (rem > 0 ? (1u << rem) - 1u : 0u);
