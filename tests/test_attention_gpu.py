@@ -700,3 +700,44 @@ def test_deep4096_all_heads_row_slices_against_the_oracle(fst):
         o = fst.fst_attention(q.cuda(), k.cuda(), v.cuda(), meta, sm_scale=w.sm_scale, kernel=kern).cpu()
         assert maxabs(o[:, :, rows], exact) <= TOL_F16, kern
     assert fst.last_status() == 0
+
+
+def test_output_delivered_to_several_copies_of_the_full_tensor(fst):
+    """fst_attention_fwd_scatter on one GPU: the "ranks'" copies of the full output are three
+    tensors of this device, and a shard's rows must land in all of them at the shard's (tree, head)
+    origin - by trees and by heads - leaving every other element untouched."""
+    import ctypes
+    from fstattention_b200 import configs
+
+    class Copies:                                        # what sharding.GatheredOutput hands to fst_attention
+        def __init__(self, tensors, rank, z0, h0):
+            self.local, self.n_ranks, self.rank, self.z0, self.h0 = tensors[rank], len(tensors), rank, z0, h0
+            self.pointer_array = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+    trees = configs.jittered_forest(7, 6, 256)
+    T, H, N, D = len(trees), 8, 256, 128
+    q, k, v = (x.cuda() for x in make_qkv(T, H, N, N, D, torch.float16, seed=71))
+    meta_all = fst.build_tree_metadata(trees, 64, 64)
+    for kern in ("auto", "tma_t32", "tma_t64"):
+        want = fst.fst_attention(q, k, v, meta_all, sm_scale=D ** -0.5, kernel=kern)    # same tile width, same bits
+        copies = [torch.full((T, H, N, D), 7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+        # trees 2..3 as one shard, written by "rank" 1
+        meta = fst.build_tree_metadata(trees[2:4], 64, 64)
+        got = fst.fst_attention(q[2:4], k[2:4], v[2:4], meta, sm_scale=D ** -0.5, kernel=kern,
+                                scatter=Copies(copies, 1, 2, 0))
+        assert got.data_ptr() == copies[1].data_ptr()
+        # heads 5..7 of every tree as another shard, written by "rank" 2
+        fst.fst_attention(q[:, 5:8], k[:, 5:8], v[:, 5:8], meta_all, sm_scale=D ** -0.5, kernel=kern,
+                          scatter=Copies(copies, 2, 0, 5))
+        torch.cuda.synchronize()
+        for c in copies:
+            assert torch.equal(c[2:4, :5], want[2:4, :5]) and torch.equal(c[:, 5:8], want[:, 5:8]), kern
+            rest = c.clone()
+            rest[2:4] = 7.0
+            rest[:, 5:8] = 7.0
+            assert (rest == 7.0).all(), kern
+    with pytest.raises(ValueError, match="shared prefix"):      # no shared prefix on this path
+        fst.fst_attention(q[:1], torch.cat((k[:1], k[:1]), 2), torch.cat((v[:1], v[:1]), 2),
+                          fst.build_tree_metadata(trees[0], 64, 64), sm_scale=1.0,
+                          scatter=Copies(copies, 0, 0, 0))
+    assert fst.last_status() == 0
