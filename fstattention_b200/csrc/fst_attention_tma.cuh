@@ -68,6 +68,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
 }
 
+// ask for one box of a rank-4 tensor to be brought into L2 (nothing is returned to the SM)
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];\n"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // one box from shared memory back to a rank-4 tensor; rows past the end of the tensor are dropped
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];\n"
@@ -172,6 +178,23 @@ attn_tma_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm_q,
     // one precompute per decode step, then one attention call per layer - and then the index
     // list, the count and the mask words are requested while the grid ahead is still draining.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    // Small grids (the 64-column instantiations): a CTA that is resident before the launch ahead of
+    // it has finished asks for its Q and its block's K/V rows to be brought into L2 meanwhile.  No
+    // value reaches the SM before the dependency wait below, and L2 is where the other launch's
+    // writes land too, so whatever it still writes to those rows is what the loads after the wait see.
+    if (TN == 64 && tid == 0) {
+        const int hk0 = h / a.kv_group;
+#pragma unroll
+        for (int j = 0; j < NB32; ++j)
+#pragma unroll
+            for (int hf = 0; hf < TL::HALVES; ++hf) {
+                tma_prefetch_4d(&tm_q, hf * 64, row0 + j * 32, h, z);
+                if (tree) {
+                    tma_prefetch_4d(&tm_k, hf * 64, prefix + row0 + j * 32, hk0, z);
+                    tma_prefetch_4d(&tm_v, hf * 64, prefix + row0 + j * 32, hk0, z);
+                }
+            }
+    }
     const bool early_meta = a.meta_stable != 0;
     if (!early_meta) asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
