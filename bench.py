@@ -985,8 +985,8 @@ def run_reference_triton(args, rank, world):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     cases = [("medusa256", configs.workload("medusa256"), 40), ("forest64", configs.workload("forest64"), 2)]
-    for n_ctx in (1024, 4096, 16384):
-        cases.append((f"sweep{n_ctx}", sweep_workload(configs, fst, n_ctx), max(2, 65536 // n_ctx)))
+    for n_ctx in (2 ** i for i in range(10, 17)):            # the reference's own x axis (fstattention.py:245)
+        cases.append((f"sweep{n_ctx}", sweep_workload(configs, fst, n_ctx), max(2, 32768 // n_ctx)))
     ref = reference_triton_times(cases, dev)
     ours = {}
     if "unavailable" not in ref:
